@@ -9,7 +9,9 @@ size than its keys keeps two tensors, ``[layers, pages, kv_heads, page_size, hea
 (the reference's pool works that way for its single group, ``cache/block_pool.py:332-351``;
 its free list is LIFO as well, ``:570,735-757``).  Groups with a window give pages back as
 soon as every position in them has fallen out of every future query's window; the table
-keeps ``-1`` there, and kernels never look below the window.
+keeps ``-1`` there, and kernels never look below the window.  Groups whose queries read their
+own chunk of positions only (``chunk``) give back the pages that lie wholly before the chunk of
+the next position in the same way.
 
 *Requests.*  ``add_request`` hands out a stable slot (requests never move when another one
 ends, unlike the reference's ``remove_request`` which shifts indices,
@@ -89,6 +91,7 @@ class GroupSpec:
     head_dim: int
     window: int | None
     value_dim: int | None = None   # size of a value per head where it differs from head_dim (0: keys only)
+    chunk: int | None = None       # queries read the keys of their own chunk of this many positions only
 
 
 @dataclass
@@ -119,12 +122,13 @@ def group_needs(needs: Sequence) -> list[GroupSpec]:
         if n.kv is None:
             continue
         vdim = getattr(n.kv, "value_dim", None)
-        key = (n.kv.kv_heads, n.kv.head_dim, n.kv.window, None if vdim in (None, n.kv.head_dim) else vdim)
+        key = (n.kv.kv_heads, n.kv.head_dim, n.kv.window, None if vdim in (None, n.kv.head_dim) else vdim,
+               getattr(n.kv, "chunk", None))
         if key not in members:
             members[key] = []
             order.append(key)
         members[key].append(n.index)
-    return [GroupSpec(tuple(members[k]), k[0], k[1], k[2], k[3]) for k in order]
+    return [GroupSpec(tuple(members[k]), k[0], k[1], k[2], k[3], k[4]) for k in order]
 
 
 class CacheManager:
@@ -156,7 +160,7 @@ class CacheManager:
             if len(pages) != len(self.groups):
                 raise CacheError(f"{len(self.groups)} groups but {len(pages)} page counts")
         self.pools = [PagePool(n) for n in pages]
-        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None]
+        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None or g.chunk is not None]
         self._requests: dict[Hashable, _Request] = {}
         self._free_slots = list(range(max_requests - 1, -1, -1))
 
@@ -173,7 +177,7 @@ class CacheManager:
         cap = None if max_request_tokens is None else -(-int(max_request_tokens) // page_size)
         self.table_width = []
         for g, n in zip(self.groups, pages):
-            widest = n if g.window is None else max(n, 65536 if cap is None else cap)
+            widest = n if (g.window is None and g.chunk is None) else max(n, 65536 if cap is None else cap)
             self.table_width.append(max(1, widest if cap is None else min(widest, cap)))
         # pages handed out since the last take_table_updates(): flat (slot, index, page) triples
         self._table_updates: list[list[int]] = [[] for _ in self.groups]
@@ -275,12 +279,12 @@ class CacheManager:
 
     def _window_release_count(self, gi: int, length: int) -> int:
         """Leading pages of a request holding ``length`` tokens that no future query reads."""
-        w = self.groups[gi].window
-        if w is None:
-            return 0
-        first_needed = length - w + 1      # the next query sits at position >= length
-        if first_needed <= 0:
-            return 0
+        g = self.groups[gi]
+        first_needed = 0                   # the next query sits at position >= length
+        if g.window is not None:
+            first_needed = max(first_needed, length - g.window + 1)
+        if g.chunk is not None:            # it reads from the start of its own chunk on
+            first_needed = max(first_needed, (length // g.chunk) * g.chunk)
         return first_needed // self.page_size
 
     def pages_needed(self, entries: Iterable[tuple[Hashable, int]]) -> list[int]:
@@ -292,7 +296,7 @@ class CacheManager:
             want = -(-(req.length + n_new) // self.page_size)
             for gi, g in enumerate(self.groups):
                 need[gi] += max(0, want - len(req.tables[gi]))
-                if g.window is not None:
+                if g.window is not None or g.chunk is not None:
                     need[gi] -= max(0, self._window_release_count(gi, req.length) - req.released[gi])
         return need
 

@@ -6,7 +6,8 @@
 // 32, so a row's arithmetic never depends on what else is in the batch), and keeps an
 // online softmax in fp32.  Keys and values are fetched through the block table; a
 // query at absolute position p sees keys j with  max(0, p - window + 1) <= j <= p
-// (window = 0: all keys up to p).  Keys and values may have different sizes per head (d for
+// (window = 0: all keys up to p), and with chunk > 0 only those of its own chunk of positions,
+// j >= (p / chunk) * chunk.  Keys and values may have different sizes per head (d for
 // queries and keys, dv for values and the output); keys of any size that fits in shared memory
 // and values up to 512 are taken, sizes that are no multiple of 4 element by element.
 //
@@ -42,7 +43,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ q_start, const int* __restrict__ q_len,
                          const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                          const int* __restrict__ tile_tok0, int nq, int nkv, int d, int dv, float scale,
-                         int window, const float* __restrict__ sinks, const float* __restrict__ slopes,
+                         int window, int chunk, const float* __restrict__ sinks, const float* __restrict__ slopes,
                          int v_prefix) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(16) float smem[];
@@ -66,7 +67,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int rows = min(BQ, ql - tok0);
   const int p0 = kl - ql + tok0;  // absolute position of the tile's first query
   const int j_end = p0 + rows;    // one past the last visible key
-  const int j_lo = window > 0 ? max(0, p0 - window + 1) : 0;
+  int j_lo = window > 0 ? max(0, p0 - window + 1) : 0;   // the first row's bound is the lowest of the tile
+  if (chunk > 0) j_lo = max(j_lo, (p0 / chunk) * chunk);
   const int dp = d + 1;
   const float* Vrows = v_prefix ? Ks : Vs;   // where the PV product finds a key's value, and its row pitch
   const int vpitch = v_prefix ? dp : dvp;
@@ -79,7 +81,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 
   const int r = tid >> 3, c = tid & 7;
   const int prow = p0 + r;
-  const int lo_r = window > 0 ? max(0, prow - window + 1) : 0;
+  int lo_r = window > 0 ? max(0, prow - window + 1) : 0;
+  if (chunk > 0) lo_r = max(lo_r, (prow / chunk) * chunk);
   float m_i = -INFINITY, l_i = 0.f;
   float acc[DMAX / 8];
 #pragma unroll
@@ -216,7 +219,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
                   const void* vcache, const int* block_table, int bt_stride, const int* table_rows, int page_size,
                   const int* q_start, const int* q_len, const int* kv_len, const int* tile_req,
                   const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv, float scale, int window,
-                  const float* sinks, const float* slopes, int v_prefix, cudaStream_t stream) {
+                  int chunk, const float* sinks, const float* slopes, int v_prefix, cudaStream_t stream) {
   const size_t smem = ((v_prefix ? 0 : (size_t)BK * ((dv + 3) & ~3)) + (size_t)BQ * d + (size_t)BK * (d + 1) + BQ * BK) *
                           sizeof(float) + 2 * BK * sizeof(int);
   auto kern = attention_generic_kernel<T, DMAX>;
@@ -228,21 +231,22 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
   dim3 grid((unsigned)(n_tiles * nq));
   MI_LAUNCH((kern), grid, NTHREADS, smem, stream, (const T*)q, q_stride, (T*)out, out_stride, (const T*)kcache,
                                          (const T*)vcache, block_table, bt_stride, table_rows, page_size, q_start,
-                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, dv, scale, window, sinks, slopes,
-                                         v_prefix);
+                                         q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, dv, scale, window, chunk, sinks,
+                                         slopes, v_prefix);
   return 0;
 }
 
 extern "C" int mi_attention_generic_tile_tokens() { return BQ; }
 
-extern "C" int mi_attention_generic_ext(const void* q, int q_stride, void* out, int out_stride,
-                                        const void* kcache, const void* vcache, const int* block_table,
-                                        int bt_stride, const int* table_rows, int page_size, const int* q_start,
-                                        const int* q_len, const int* kv_len, const int* tile_req,
-                                        const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
-                                        float scale, int window, const float* sinks, const float* slopes,
-                                        int v_prefix, int dtype, cudaStream_t stream) {
+extern "C" int mi_attention_generic_masked(const void* q, int q_stride, void* out, int out_stride,
+                                           const void* kcache, const void* vcache, const int* block_table,
+                                           int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                           const int* q_len, const int* kv_len, const int* tile_req,
+                                           const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
+                                           float scale, int window, int chunk, const float* sinks,
+                                           const float* slopes, int v_prefix, int dtype, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (chunk < 0) MI_REFUSE("attention: bad chunk size %d", chunk);
   if (d <= 0 || d > 1024 || dv <= 0 || dv > 512)
     MI_REFUSE("attention: head sizes %d (keys, up to 1024) and %d (values, up to 512) are not taken", d, dv);
   if (v_prefix && dv > d) MI_REFUSE("attention: values of %d cannot be the first columns of keys of %d", dv, d);
@@ -256,7 +260,7 @@ extern "C" int mi_attention_generic_ext(const void* q, int q_stride, void* out, 
 #define MI_GO(T, DMAX)                                                                              \
   rc = launch<T, DMAX>(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride,        \
                        table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, dv, \
-                       scale, window, sinks, slopes, v_prefix, stream)
+                       scale, window, chunk, sinks, slopes, v_prefix, stream)
   if (dtype == MI_DTYPE_F32) {
     if (dv <= 64) MI_GO(float, 64);
     else if (dv <= 128) MI_GO(float, 128);
@@ -274,6 +278,18 @@ extern "C" int mi_attention_generic_ext(const void* q, int q_stride, void* out, 
   if (rc == MI_REFUSED - 1) MI_REFUSE("attention: keys of %d and values of %d do not fit in shared memory", d, dv);
   if (rc) return rc;
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_attention_generic_ext(const void* q, int q_stride, void* out, int out_stride,
+                                        const void* kcache, const void* vcache, const int* block_table,
+                                        int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                        const int* q_len, const int* kv_len, const int* tile_req,
+                                        const int* tile_tok0, int n_tiles, int nq, int nkv, int d, int dv,
+                                        float scale, int window, const float* sinks, const float* slopes,
+                                        int v_prefix, int dtype, cudaStream_t stream) {
+  return mi_attention_generic_masked(q, q_stride, out, out_stride, kcache, vcache, block_table, bt_stride, table_rows,
+                                     page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles, nq, nkv, d, dv,
+                                     scale, window, 0, sinks, slopes, v_prefix, dtype, stream);
 }
 
 extern "C" int mi_attention_generic_kv(const void* q, int q_stride, void* out, int out_stride,

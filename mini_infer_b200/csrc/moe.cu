@@ -1,8 +1,9 @@
 // Routed experts: every token goes through the `top` experts its router picks.
 //
 //   mi_moe_select     from the router logits z = W_r x (fp32, a matrix product): the `top` largest of a token
-//                     (ties: the lower index) and the softmax over those alone -> ids [M, top] int32,
-//                     weights [M, top] fp32
+//                     (ties: the lower index; optionally among the experts of the best groups only) and
+//                     their weights (the softmax over those alone, or their share of the softmax over all
+//                     experts, times a factor) -> ids [M, top] int32, weights [M, top] fp32
 //   mi_moe_plan       sorts the M*top (token, choice) entries by expert: perm[pos] = entry, inv[entry] =
 //                     pos, offsets[E + 1], and the list of row tiles (expert, first row, rows) that the
 //                     grouped products walk.  Nothing comes back to the host: the products are launched
@@ -14,7 +15,8 @@
 //   mi_moe_combine    out[t, :] = T(sum_k weight[t, k] * y[inv[t*top + k], :] + shared[t, :])
 //   mi_clamped_glu    the same activation for a dense expert: out = glu(gu[:, :I], gu[:, I:])
 //
-// glu(g, u) = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit).
+// glu(g, u) = g' * sigmoid(alpha * g') * (u' + offset), g' = min(g, limit), u' = clamp(u, -limit, limit).
+// An infinite limit with alpha = 1 and offset = 0 is the plain silu(g) * u.
 //
 // Three products live here, all with fp32 accumulation, and none lets a row's result depend on which
 // other rows share its tile: float32 on CUDA cores, k ascending (moe_gemm_kernel); bfloat16 tiles of 64
@@ -26,19 +28,24 @@
 
 MI_DEFINE_ERROR_API()
 
-__device__ __forceinline__ float mi_clamped_glu_value(float g, float u, float limit, float alpha) {
+__device__ __forceinline__ float mi_clamped_glu_value(float g, float u, float limit, float alpha, float offset) {
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
-  return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + offset);
 }
 
 // ------------------------------------------------------------------------------------------ router
 // The logits [M, E] (fp32) come from a matrix product; one warp per token picks the `top` largest
-// (ties: the lower index) and takes the softmax over those alone.
+// (ties: the lower index).  Two ways to weigh them.  all_scores = 0: the softmax over the chosen logits
+// alone.  all_scores = 1: scores are the softmax over all experts; the chosen experts' scores are divided
+// by their sum (+ 1e-20) and multiplied by `scale`.  With n_groups > 1 the experts lie in n_groups equal
+// groups of neighbours, a group counts as its best expert, and only experts of the `keep` best groups
+// (ties: the lower index) can be chosen.
 #define ROUTE_MAX_PER_LANE 8
 
 __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, int* __restrict__ ids,
-                                  float* __restrict__ weights, int M, int E, int top) {
+                                  float* __restrict__ weights, int M, int E, int top, int all_scores, int n_groups,
+                                  int keep, float scale) {
   mi_pdl_enter();
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -49,6 +56,57 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
   for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     lg[i] = e < E ? z[e] : -INFINITY;
+  }
+  float zmax = -INFINITY, zsum = 0.f;
+  if (all_scores) {
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) zmax = fmaxf(zmax, lg[i]);
+    zmax = mi_warp_max(zmax);
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+      if (lane + 32 * i < E) zsum += expf(lg[i] - zmax);
+    zsum = mi_warp_sum(zsum);
+  }
+  if (n_groups > 1) {
+    // the groups that stay: `keep` times the best group that is still in, by its best logit (the
+    // softmax keeps the order); experts of the others are taken out
+    const int per = E / n_groups;
+    unsigned long long kept_lo = 0ull, kept_hi[3] = {0ull, 0ull, 0ull};   // up to 256 groups, one bit each
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        if (e >= E) continue;
+        const int g = e / per;
+        const bool taken = g < 64 ? (kept_lo >> g) & 1ull : (kept_hi[(g >> 6) - 1] >> (g & 63)) & 1ull;
+        if (!taken && (lg[i] > best || (lg[i] == best && g < best_g))) {
+          best = lg[i];
+          best_g = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ob > best || (ob == best && og < best_g)) {
+          best = ob;
+          best_g = og;
+        }
+      }
+      if (best_g == 0x7fffffff) break;
+      if (best_g < 64) kept_lo |= 1ull << best_g;
+      else kept_hi[(best_g >> 6) - 1] |= 1ull << (best_g & 63);
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e >= E) continue;
+      const int g = e / per;
+      const bool in = g < 64 ? (kept_lo >> g) & 1ull : (kept_hi[(g >> 6) - 1] >> (g & 63)) & 1ull;
+      if (!in) lg[i] = -INFINITY;
+    }
   }
   float my_val = 0.f, denom = 0.f, first = 0.f;
   int my_id = 0;
@@ -76,7 +134,7 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
       if (best_e == lane + 32 * i) lg[i] = -INFINITY;   // taken
     if (k == 0) first = best;
-    const float p = expf(best - first);
+    const float p = all_scores ? expf(best - zmax) / zsum : expf(best - first);
     denom += p;
     if (lane == k) {
       my_val = p;
@@ -85,16 +143,22 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
   }
   if (lane < top) {
     ids[(size_t)t * top + lane] = my_id;
-    weights[(size_t)t * top + lane] = my_val / denom;
+    weights[(size_t)t * top + lane] = all_scores ? my_val / (denom + 1e-20f) * scale : my_val / denom;
   }
 }
 
 extern "C" int mi_moe_select(const float* logits, int stride, int* ids, float* weights, int M, int E, int top,
-                             cudaStream_t stream) {
+                             int all_scores, int n_groups, int keep, float scale, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE) MI_REFUSE("moe: %d experts (1 to %d are taken)", E, 32 * ROUTE_MAX_PER_LANE);
   if (top <= 0 || top > E || top > 32) MI_REFUSE("moe: %d of %d experts per token", top, E);
-  MI_LAUNCH((moe_select_kernel), (M + 3) / 4, 128, 0, stream, logits, stride, ids, weights, M, E, top);
+  if (n_groups > 1) {
+    if (E % n_groups) MI_REFUSE("moe: %d experts are no %d equal groups", E, n_groups);
+    if (keep <= 0 || keep > n_groups) MI_REFUSE("moe: %d of %d groups kept", keep, n_groups);
+    if (keep * (E / n_groups) < top) MI_REFUSE("moe: %d groups of %d experts cannot give %d experts", keep, E / n_groups, top);
+  }
+  MI_LAUNCH((moe_select_kernel), (M + 3) / 4, 128, 0, stream, logits, stride, ids, weights, M, E, top, all_scores,
+            n_groups, keep, scale);
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -162,7 +226,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0, const T* __restrict__ w1,
                 long long w_expert_stride, const int* __restrict__ perm, int top, const int* __restrict__ plan,
-                int E, void* __restrict__ out_, int N, int K, float limit, float alpha) {
+                int E, void* __restrict__ out_, int N, int K, float limit, float alpha, float offset) {
   mi_pdl_enter();
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
@@ -232,7 +296,7 @@ moe_gemm_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ w0,
       if (n >= N) continue;
       if (GATED)
         reinterpret_cast<T*>(out_)[(size_t)(row0 + r) * N + n] =
-            mi_from_float<T>(mi_clamped_glu_value(acc0[i][j], acc1[i][j], limit, alpha));
+            mi_from_float<T>(mi_clamped_glu_value(acc0[i][j], acc1[i][j], limit, alpha, offset));
       else
         reinterpret_cast<float*>(out_)[(size_t)(row0 + r) * N + n] = acc0[i][j];
     }
@@ -279,7 +343,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                     long long w_expert_stride, const int* __restrict__ perm, int top, const int* __restrict__ plan,
-                    int E, void* __restrict__ out_, int N, int K, float limit, float alpha, int vec) {
+                    int E, void* __restrict__ out_, int N, int K, float limit, float alpha, float offset, int vec) {
   mi_pdl_enter();
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
@@ -360,7 +424,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __rest
         if (r >= rows || n >= N) continue;
         if (GATED)
           reinterpret_cast<bf16*>(out_)[(size_t)(row0 + r) * N + n] =
-              __float2bfloat16_rn(mi_clamped_glu_value(acc0[i][j][c], acc1[i][j][c], limit, alpha));
+              __float2bfloat16_rn(mi_clamped_glu_value(acc0[i][j][c], acc1[i][j][c], limit, alpha, offset));
         else
           reinterpret_cast<float*>(out_)[(size_t)(row0 + r) * N + n] = acc0[i][j][c];
       }
@@ -391,7 +455,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(256)
 moe_stream_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                   long long w_expert_stride, const int* __restrict__ perm, int top, const int* __restrict__ plan,
-                  int E, void* __restrict__ out_, int N, int K, float limit, float alpha) {
+                  int E, void* __restrict__ out_, int N, int K, float limit, float alpha, float offset) {
   mi_pdl_enter();
   const int tile = blockIdx.y;
   if (tile >= plan[0]) return;
@@ -439,7 +503,7 @@ moe_stream_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restri
       if (lane == 0) {
         if (GATED)
           reinterpret_cast<bf16*>(out_)[(size_t)(row0 + r) * N + n] =
-              __float2bfloat16_rn(mi_clamped_glu_value(s0, s1, limit, alpha));
+              __float2bfloat16_rn(mi_clamped_glu_value(s0, s1, limit, alpha, offset));
         else
           reinterpret_cast<float*>(out_)[(size_t)(row0 + r) * N + n] = s0;
       }
@@ -451,8 +515,8 @@ static int max_tiles(int n_entries, int E, int tile_rows) { return (n_entries + 
 
 extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, const void* w_up,
                               long long w_expert_stride, const int* perm, int top, const int* plan, int E,
-                              void* act, int n_entries, int ff, int H, float limit, float alpha, int tile_rows,
-                              int dtype, cudaStream_t stream) {
+                              void* act, int n_entries, int ff, int H, float limit, float alpha, float offset,
+                              int tile_rows, int dtype, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (tile_rows == FEW_ROWS) {
     if (dtype != MI_DTYPE_BF16 || !mma_vec_ok(x, x_stride, w_gate, w_up, H))
@@ -460,17 +524,17 @@ extern "C" int mi_moe_gate_up(const void* x, int x_stride, const void* w_gate, c
     dim3 g((ff + 7) / 8, max_tiles(n_entries, E, FEW_ROWS));
     if (g.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
     MI_LAUNCH((moe_stream_kernel<true>), g, 256, 0, stream, (const bf16*)x, x_stride, (const bf16*)w_gate,
-              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha);
+              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha, offset);
     MI_RETURN_LAUNCH_STATUS();
   }
   dim3 grid((ff + TILE_N - 1) / TILE_N, max_tiles(n_entries, E, TILE_M));
   if (grid.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_gemm_kernel<float, true>), grid, 256, 0, stream, (const float*)x, x_stride, (const float*)w_gate,
-              (const float*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha);
+              (const float*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha, offset);
   else if (dtype == MI_DTYPE_BF16)
     MI_LAUNCH((moe_gemm_mma_kernel<true>), grid, 128, 0, stream, (const bf16*)x, x_stride, (const bf16*)w_gate,
-              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha,
+              (const bf16*)w_up, w_expert_stride, perm, top, plan, E, act, ff, H, limit, alpha, offset,
               mma_vec_ok(x, x_stride, w_gate, w_up, H));
   else
     MI_REFUSE("moe: unknown dtype %d", dtype);
@@ -486,17 +550,17 @@ extern "C" int mi_moe_down(const void* act, const void* w_down, long long w_expe
     dim3 g((H + 7) / 8, max_tiles(n_entries, E, FEW_ROWS));
     if (g.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
     MI_LAUNCH((moe_stream_kernel<false>), g, 256, 0, stream, (const bf16*)act, ff, (const bf16*)w_down,
-              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f);
+              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f, 0.f);
     MI_RETURN_LAUNCH_STATUS();
   }
   dim3 grid((H + TILE_N - 1) / TILE_N, max_tiles(n_entries, E, TILE_M));
   if (grid.y > 65535) MI_REFUSE("moe: too many row tiles for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_gemm_kernel<float, false>), grid, 256, 0, stream, (const float*)act, ff, (const float*)w_down,
-              (const float*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f);
+              (const float*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f, 0.f);
   else if (dtype == MI_DTYPE_BF16)
     MI_LAUNCH((moe_gemm_mma_kernel<false>), grid, 128, 0, stream, (const bf16*)act, ff, (const bf16*)w_down,
-              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f,
+              (const bf16*)nullptr, w_expert_stride, (const int*)nullptr, 1, plan, E, (void*)y, H, ff, 0.f, 0.f, 0.f,
               mma_vec_ok(act, ff, w_down, nullptr, ff));
   else
     MI_REFUSE("moe: unknown dtype %d", dtype);
@@ -573,25 +637,25 @@ extern "C" int mi_moe_combine(const void* y, int y_dtype, const int* inv, const 
 // ------------------------------------------------------------------------------------------ dense expert
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, int stride, T* __restrict__ out, int M, int I,
-                                   float limit, float alpha) {
+                                   float limit, float alpha, float offset) {
   mi_pdl_enter();
   const size_t n = (size_t)M * I;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / I), c = (int)(idx - (size_t)t * I);
     const float g = mi_to_float(gu[(size_t)t * stride + c]), u = mi_to_float(gu[(size_t)t * stride + I + c]);
-    out[idx] = mi_from_float<T>(mi_clamped_glu_value(g, u, limit, alpha));
+    out[idx] = mi_from_float<T>(mi_clamped_glu_value(g, u, limit, alpha, offset));
   }
 }
 
 extern "C" int mi_clamped_glu(const void* gu, int stride, void* out, int M, int I, float limit, float alpha,
-                              int dtype, cudaStream_t stream) {
+                              float offset, int dtype, cudaStream_t stream) {
   if (M <= 0 || I <= 0) return 0;
   const size_t n = (size_t)M * I;
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   if (dtype == MI_DTYPE_F32)
-    MI_LAUNCH((clamped_glu_kernel<float>), blocks, 256, 0, stream, (const float*)gu, stride, (float*)out, M, I, limit, alpha);
+    MI_LAUNCH((clamped_glu_kernel<float>), blocks, 256, 0, stream, (const float*)gu, stride, (float*)out, M, I, limit, alpha, offset);
   else if (dtype == MI_DTYPE_BF16)
-    MI_LAUNCH((clamped_glu_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gu, stride, (bf16*)out, M, I, limit, alpha);
+    MI_LAUNCH((clamped_glu_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gu, stride, (bf16*)out, M, I, limit, alpha, offset);
   else
     MI_REFUSE("moe: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

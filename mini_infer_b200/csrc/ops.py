@@ -152,6 +152,10 @@ def _sig_attention_generic(lib: ctypes.CDLL) -> None:
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.mi_attention_generic_masked.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -223,13 +227,13 @@ def _sig_rope_norm(lib: ctypes.CDLL) -> None:
                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                        c_int, c_int, c_void_p]
     lib.mi_gate_mul.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                c_int, c_void_p]
+                                c_int, c_int, c_void_p]
 
 
 def _sig_recurrent(lib: ctypes.CDLL) -> None:
     ll = ctypes.c_longlong
     lib.mi_causal_conv.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, ll, c_void_p, c_void_p,
-                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_rglru_scan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, ll, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
@@ -241,7 +245,11 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mi_rglru_chunked_scratch.restype = ll
     lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+                                c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
+    lib.mi_delta_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_float, c_float, c_void_p, ll, ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_void_p]
     lib.mi_gla_chunked_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mi_gla_chunked_scratch.restype = ll
     lib.mi_headnorm_gate.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -250,18 +258,19 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
 
 def _sig_moe(lib: ctypes.CDLL) -> None:
     ll = ctypes.c_longlong
-    lib.mi_moe_select.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mi_moe_select.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_float, c_void_p]
     lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.mi_moe_tile_rows.argtypes = [c_int]
     lib.mi_moe_tile_rows.restype = c_int
     lib.mi_moe_gate_up.argtypes = [c_void_p, c_int, c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int,
-                                   c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]
+                                   c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_void_p]
     lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p]
     lib.mi_moe_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                    c_int, c_void_p]
     lib.mi_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
-    lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p]
+    lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p]
 
 
 def _sig_stream(lib: ctypes.CDLL) -> None:
@@ -272,6 +281,8 @@ def _sig_stream(lib: ctypes.CDLL) -> None:
     lib.mi_add_rmsnorm_multi.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]
     lib.mi_glu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mi_embedding_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                                         c_void_p]
 
 
 def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
@@ -281,6 +292,12 @@ def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
     lib.mi_latent_prepare.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_void_p]
+
+
+    lib.mi_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_float, c_float,
+                                          c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_void_p]
 
 
 def _sig_attention_rows(lib: ctypes.CDLL) -> None:
@@ -1216,17 +1233,20 @@ def rope_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
 _ACT = {"sigmoid": 1, "silu": 2, None: 0}
 
 
-def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, act: str, scale: float = 1.0) -> None:
-    """``out = x * act(gate) * scale`` element by element; all three ``[M, C]`` (column ranges of
-    wider tensors are fine), ``act`` ``"sigmoid"`` or ``"silu"``, fp32 arithmetic."""
+def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, act: str, scale: float = 1.0,
+             per: int = 1) -> None:
+    """``out = x * act(gate) * scale`` element by element; ``x`` and ``out`` ``[M, C]`` (column ranges of
+    wider tensors are fine), ``act`` ``"sigmoid"`` or ``"silu"``, fp32 arithmetic.  ``per`` > 1: one gate
+    for every ``per`` neighbouring columns (a gate per head), ``gate`` being ``[M, C / per]``."""
     _cuda(x, gate, out)
     for t in (x, gate, out):
         _cols(t, "gate_mul")
-    if x.shape != gate.shape or x.shape != out.shape or not (x.dtype == gate.dtype == out.dtype):
-        raise KernelError("gate_mul: x, gate and out must agree in shape and dtype")
+    if (per <= 0 or x.shape[1] % per or tuple(gate.shape) != (x.shape[0], x.shape[1] // per) or x.shape != out.shape
+            or not (x.dtype == gate.dtype == out.dtype)):
+        raise KernelError("gate_mul: x and out must agree in shape, the gate has a column per group, one dtype")
     lib = _lib("rope_norm")
     rc = lib.mi_gate_mul(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), x.shape[0],
-                         x.shape[1], _ACT[act], float(scale), _code(x.dtype), _stream())
+                         x.shape[1], _ACT[act], float(scale), int(per), _code(x.dtype), _stream())
     _finish(lib, rc, "gate_mul")
 
 
@@ -1274,11 +1294,14 @@ def _f32vec(t: torch.Tensor | None, n: int, what: str) -> None:
 
 
 def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
-                state: torch.Tensor, ctx, out: torch.Tensor) -> None:
+                state: torch.Tensor, ctx, out: torch.Tensor, act: str | None = None) -> None:
     """Per channel ``out[t] = bias + sum_j weight[:, j] * in[t - (taps - 1 - j)]`` with ``in = x +
     x_bias``; the ``taps - 1`` inputs before a request's portion come from the head of its state
     row (``[taps - 1, C]``, oldest first; zeros at the start of a sequence).  The state is read
-    only (``rglru_scan`` moves it on)."""
+    only (the scan behind it moves it on: ``rglru_scan``, ``delta_scan``).  ``act`` ``"silu"``: the SiLU of
+    the sum is written."""
+    if act not in (None, "silu"):
+        raise KernelError(f"causal_conv: unknown activation {act!r}")
     _cuda(x, x_bias, weight, bias, state, out)
     _cols(x, "causal_conv")
     _cols(out, "causal_conv")
@@ -1294,7 +1317,8 @@ def causal_conv(x: torch.Tensor, x_bias: torch.Tensor | None, weight: torch.Tens
     lib = _lib("recurrent")
     rc = lib.mi_causal_conv(_ptr(x), x.stride(0), _ptr(x_bias), _ptr(weight), _ptr(bias), _ptr(state), stride,
                             _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(out), out.stride(0),
-                            ctx.n_requests, _max_q_len(ctx), C, taps, _code(x.dtype), _stream())
+                            ctx.n_requests, _max_q_len(ctx), C, taps, 1 if act == "silu" else 0, _code(x.dtype),
+                            _stream())
     _finish(lib, rc, "causal_conv")
 
 
@@ -1358,22 +1382,28 @@ def rglru_scan(gates: torch.Tensor, gate_bias_r: torch.Tensor, gate_bias_i: torc
 GLA_CHUNK = 128      # tokens per chunk of the chunked walk of gated linear attention
 
 
-def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor | None,
-             tau: float, q_scale: float, heads: int, dk: int, dv: int, state: torch.Tensor, ctx) -> torch.Tensor:
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor | None, z_bias: torch.Tensor | None,
+             tau: float, q_scale: float, heads: int, dk: int, dv: int, state: torch.Tensor, ctx,
+             head_decay: torch.Tensor | None = None) -> torch.Tensor:
     """Gated linear attention over each request's portion, from and into its state row
     ``[heads, dk, dv]``: ``S = diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)`` with
     ``alpha = sigmoid(z + z_bias)^(1 / tau)``.  q, k, v: column ranges of one packed projection;
-    ``z`` fp32 ``[M, heads * dk]``.  Returns fp32 ``o [M, heads * dv]``."""
-    _cuda(q, k, v, z, z_bias, state)
-    for t in (q, k, v, z):
+    ``z`` fp32 ``[M, heads * dk]``.  With ``head_decay`` (fp32 ``[heads]``) every head has one fixed
+    decay in the place of ``alpha`` and ``z`` is not read (linear attention with a fixed decay, or
+    retention).  Returns fp32 ``o [M, heads * dv]``."""
+    _cuda(q, k, v, z, z_bias, state, head_decay)
+    for t in (q, k, v) + ((z,) if z is not None else ()):
         _cols(t, "gla")
     M = q.shape[0]
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or not (q.dtype == k.dtype == v.dtype):
         raise KernelError("gla: q, k and v must be column ranges of one packed projection")
     if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv:
         raise KernelError("gla: q, k must be [M, heads * dk] and v [M, heads * dv]")
-    if z.dtype != torch.float32 or z.shape != (M, heads * dk):
+    if head_decay is None and z is None:
+        raise KernelError("gla: needs z (a decay per channel) or head_decay (one per head)")
+    if z is not None and (z.dtype != torch.float32 or z.shape != (M, heads * dk)):
         raise KernelError("gla: z must be fp32 [M, heads * dk]")
+    _f32vec(head_decay, heads, "gla")
     _f32vec(z_bias, heads * dk, "gla")
     stride = _state_rows(state, "gla")
     if stride < heads * dk * dv:
@@ -1390,11 +1420,58 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         scratch = torch.empty(lib.mi_gla_chunked_scratch(ctx.n_requests, n_chunks, heads, dk, dv), dtype=torch.float32,
                               device=q.device)
         launch_count += 1
-    rc = lib.mi_gla_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0), _ptr(z_bias), 1.0 / float(tau),
+    rc = lib.mi_gla_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
+                         _ptr(z_bias), 1.0 / float(tau),
                          float(q_scale), _ptr(state), stride, _ptr(ctx.q_start), _ptr(ctx.q_len),
                          _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _ptr(scratch),
-                         n_chunks, GLA_CHUNK, _code(q.dtype), _stream())
+                         n_chunks, GLA_CHUNK, _ptr(head_decay), _code(q.dtype), _stream())
     _finish(lib, rc, "gla")
+    return o
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, b: torch.Tensor, q_scale: float, unit_eps: float, heads: int, kv_heads: int,
+               dk: int, dv: int, state: torch.Tensor, state_offset: int, ctx, *, conv_in: torch.Tensor | None = None,
+               taps: int = 1) -> torch.Tensor:
+    """The gated delta rule over each request's portion, from and into ``S [heads, dk, dv]`` at
+    ``state_offset`` of its state row: ``S <- diag(g) S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``,
+    ``o = S^T q`` with ``q`` and ``k`` (``kv_heads`` heads of ``dk``, shared by ``heads / kv_heads`` heads
+    each) made unit vectors first (``x / sqrt(sum x^2 + unit_eps)``; ``q`` also times ``q_scale``),
+    ``g = exp(-exp(a_log) * softplus(z + dt_bias))`` per head and key channel (``z`` fp32 ``[M, heads *
+    dk]``) and ``beta = sigmoid(b)`` (``[M, heads]``).  q, k, v: column ranges of one packed tensor.
+    ``conv_in`` (``[M, C]``) with ``taps``: the inputs of the short convolution that produced q, k and
+    v; the head of the state row (``[taps - 1, C]``) is moved on to this portion's last inputs.
+    Returns fp32 ``o [M, heads * dv]``."""
+    _cuda(q, k, v, z, dt_bias, a_log, b, state, conv_in)
+    for t in (q, k, v, z, b):
+        _cols(t, "delta")
+    M = q.shape[0]
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or not (q.dtype == k.dtype == v.dtype == b.dtype):
+        raise KernelError("delta: q, k and v must be column ranges of one packed tensor")
+    if q.shape[1] != kv_heads * dk or k.shape[1] != kv_heads * dk or v.shape[1] != heads * dv or b.shape != (M, heads):
+        raise KernelError("delta: q, k must be [M, kv_heads * dk], v [M, heads * dv] and b [M, heads]")
+    if z.dtype != torch.float32 or z.shape != (M, heads * dk):
+        raise KernelError("delta: z must be fp32 [M, heads * dk]")
+    _f32vec(dt_bias, heads * dk, "delta")
+    _f32vec(a_log, heads, "delta")
+    stride = _state_rows(state, "delta")
+    C = 0
+    if conv_in is not None:
+        _cols(conv_in, "delta")
+        C = conv_in.shape[1]
+        if conv_in.dtype != q.dtype or conv_in.shape[0] != M or state_offset < (taps - 1) * C:
+            raise KernelError("delta: the convolution's inputs do not fit the state row")
+    if stride < state_offset + heads * dk * dv:
+        raise KernelError("delta: state row too short")
+    o = torch.empty((M, heads * dv), dtype=torch.float32, device=q.device)
+    lib = _lib("recurrent")
+    rc = lib.mi_delta_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0), _ptr(dt_bias), _ptr(a_log),
+                           _ptr(b), b.stride(0), float(q_scale), float(unit_eps), _ptr(state), stride,
+                           int(state_offset), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(o),
+                           o.stride(0), ctx.n_requests, heads, kv_heads, dk, dv, _ptr(conv_in),
+                           conv_in.stride(0) if conv_in is not None else 0, C, int(taps) if conv_in is not None else 1,
+                           _code(q.dtype), _stream())
+    _finish(lib, rc, "delta")
     return o
 
 
@@ -1422,9 +1499,13 @@ def headnorm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | No
 # --------------------------------------------------------------------------------------- routed experts
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Tensor, torch.Tensor]:
+def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, all_scores: bool = False, groups: int = 0,
+              keep_groups: int = 0, scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 router logits ``x router^T``; per token the ``top`` experts with the largest logits
-    (int32 ``[M, top]``, largest first) and the softmax over those logits alone (fp32)."""
+    (int32 ``[M, top]``, largest first) and their weights (fp32): the softmax over those logits alone,
+    or, with ``all_scores``, their scores under the softmax over all experts divided by the sum of
+    these (+ 1e-20), times ``scale``.  ``groups`` > 1: the experts form that many equal groups of
+    neighbours, a group counts as its best expert, and only the ``keep_groups`` best groups give experts."""
     _cuda(x, router)
     _cols(x, "moe")
     if router.dim() != 2 or router.shape[1] != x.shape[1] or router.dtype != x.dtype or not router.is_contiguous():
@@ -1435,7 +1516,8 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Te
     ids = torch.empty((M, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((M, top), dtype=torch.float32, device=x.device)
     lib = _lib("moe")
-    rc = lib.mi_moe_select(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(weights), M, E, int(top), _stream())
+    rc = lib.mi_moe_select(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(weights), M, E, int(top),
+                           1 if all_scores else 0, int(groups), int(keep_groups), float(scale), _stream())
     _finish(lib, rc, "moe_select")
     return ids, weights
 
@@ -1445,10 +1527,12 @@ USE_GROUPED_MM = os.environ.get("MINI_INFER_GROUPED_MM", "1") != "0"
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None) -> torch.Tensor:
+                w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None,
+                up_offset: float = 1.0) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) (+ shared[t])`` with
-    ``expert(x) = W_down glu(W_gate x, W_up x)``, ``glu(g, u) = g' sigmoid(alpha g') (u' + 1)``,
-    ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``.  Weights are stacked per expert:
+    ``expert(x) = W_down glu(W_gate x, W_up x)``, ``glu(g, u) = g' sigmoid(alpha g') (u' + up_offset)``,
+    ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` (an infinite ``limit`` with ``alpha`` 1 and
+    ``up_offset`` 0 is the plain ``silu(g) * u``).  Weights are stacked per expert:
     ``w_gate_up [E, 2 ff, H]`` (an expert's gate rows, then its up rows), ``w_down [E, H, ff]``.
     Entries are sorted by expert on the device; nothing is read back.  Three routes: a step that
     brings an expert only a few rows streams the weights (bfloat16); large bfloat16 steps gather
@@ -1490,14 +1574,14 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         rc = lib.mi_moe_gather(_ptr(x), x.stride(0), _ptr(perm), top, _ptr(xs), n, H, _code(x.dtype), _stream())
         _finish(lib, rc, "moe_gather")
         ends = plan[2:2 + E]                       # where each expert's rows end
-        act = clamped_glu(torch._grouped_mm(xs, w_gate_up.transpose(-2, -1), offs=ends), limit, alpha)
+        act = clamped_glu(torch._grouped_mm(xs, w_gate_up.transpose(-2, -1), offs=ends), limit, alpha, up_offset)
         y = torch._grouped_mm(act, w_down.transpose(-2, -1), offs=ends)
         launch_count += 2
     else:
         act = torch.empty((n, ff), dtype=x.dtype, device=dev)
         rc = lib.mi_moe_gate_up(_ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(w_gate_up[:, ff:]), 2 * ff * H, _ptr(perm),
-                                top, _ptr(plan), E, _ptr(act), n, ff, H, float(limit), float(alpha), tile,
-                                _code(x.dtype), _stream())
+                                top, _ptr(plan), E, _ptr(act), n, ff, H, float(limit), float(alpha), float(up_offset),
+                                tile, _code(x.dtype), _stream())
         _finish(lib, rc, "moe_gate_up")
         y = torch.empty((n, H), dtype=torch.float32, device=dev)
         rc = lib.mi_moe_down(_ptr(act), _ptr(w_down), H * ff, _ptr(plan), E, _ptr(y), n, H, ff, tile, _code(x.dtype),
@@ -1511,7 +1595,7 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     return out
 
 
-def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float, up_offset: float = 1.0) -> torch.Tensor:
     """``glu(gate_up[:, :I], gate_up[:, I:])`` of ``moe_experts`` for a dense expert."""
     _cuda(gate_up)
     _cols(gate_up, "clamped_glu")
@@ -1519,7 +1603,7 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tens
     out = torch.empty((M, I2 // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("moe")
     rc = lib.mi_clamped_glu(_ptr(gate_up), gate_up.stride(0), _ptr(out), M, I2 // 2, float(limit), float(alpha),
-                            _code(gate_up.dtype), _stream())
+                            float(up_offset), _code(gate_up.dtype), _stream())
     _finish(lib, rc, "clamped_glu")
     return out
 
@@ -1571,6 +1655,24 @@ def embedding_pair_hash(table: torch.Tensor, pair_table: torch.Tensor, ctx, last
                                     _ptr(ctx.q_len), _ptr(ctx.state_slot), _ptr(last_token), int(ctx.n_requests),
                                     _ptr(out), M, H, V, int(buckets), int(mul_prev), int(mul_cur), _code(table.dtype),
                                     _stream())
+    _finish(lib, rc, "embedding")
+    return out
+
+
+def embedding_rmsnorm(table: torch.Tensor, ids: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * gain`` with ``x = float(table[ids])`` as the fp32 residual stream
+    ``[M, H]`` (``gain`` fp32 ``[H]``): an embedding with a norm of its own."""
+    _cuda(table, ids, gain)
+    if ids.dtype != torch.int32 or ids.dim() != 1 or not ids.is_contiguous():
+        raise KernelError("embedding: ids must be a contiguous int32 vector")
+    if table.dim() != 2 or not table.is_contiguous():
+        raise KernelError("embedding: table must be a contiguous [V, H] matrix")
+    V, H = table.shape
+    _f32vec(gain, H, "embedding")
+    out = torch.empty((ids.shape[0], H), dtype=torch.float32, device=table.device)
+    lib = _lib("stream")
+    rc = lib.mi_embedding_rmsnorm(_ptr(table), _ptr(ids), _ptr(gain), _ptr(out), ids.shape[0], H, V, float(eps),
+                                  _code(table.dtype), _stream())
     _finish(lib, rc, "embedding")
     return out
 
@@ -1672,6 +1774,61 @@ def qk_bias_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int,
                                    _ptr(q_bias), _ptr(k_bias), _ptr(q_gain), _ptr(k_gain), float(eps),
                                    1 if values_are_keys else 0, _ptr(slots), _ptr(kcache), _ptr(vcache), page_size,
                                    1 if writes else 0, _code(packed.dtype), _stream())
+    _finish(lib, rc, "qk_prepare")
+
+
+def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int | None, nq: int, nkv: int, d: int,
+                       dv: int, *, q_gain: torch.Tensor | None = None, k_gain: torch.Tensor | None = None,
+                       eps: float = 0.0, rot: int = 0, positions: torch.Tensor | None = None,
+                       freq: torch.Tensor | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                       v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
+                       slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
+                       vcache: torch.Tensor | None = None) -> None:
+    """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
+    ``k_off``, ``nkv`` heads of ``d``; v at ``v_off``, ``nkv`` heads of ``dv``, or ``v_off`` None: no values
+    here): q and k get an RMS norm over the head with the gain shared by the heads (fp32 ``[d]``; None:
+    no norm), then the rotation of the half layout on their first ``rot`` dimensions (``freq`` float64
+    ``[rot / 2]``; the angle in double precision), then the factors ``q_scale`` / ``k_scale``; both are
+    written back.  With ``v_other`` (``[M, nkv * dv]``) and ``blend`` (fp32, one element) the values
+    become ``(1 - blend) v + blend v_other`` and are written back too.  With caches, k and v are stored
+    at ``slots``."""
+    _cuda(packed, q_gain, k_gain, positions, freq, v_other, blend, slots, kcache, vcache)
+    _cols(packed, "qk_prepare")
+    M, width = packed.shape
+    has_v = v_off is not None
+    if q_off + nq * d > width or k_off + nkv * d > width or (has_v and v_off + nkv * dv > width):
+        raise KernelError("qk_prepare: a column range lies outside the packed projection")
+    _opt_f32(q_gain, d, "qk_prepare (q gain)")
+    _opt_f32(k_gain, d, "qk_prepare (k gain)")
+    if rot:
+        if positions is None or positions.dtype != torch.int32 or positions.shape != (M,):
+            raise KernelError("qk_prepare: positions must be int32 [M]")
+        if freq is None or freq.dtype != torch.float64 or freq.shape != (rot // 2,) or not freq.is_contiguous():
+            raise KernelError("qk_prepare: freq must be float64 [rot / 2]")
+    if v_other is not None:
+        _cols(v_other, "qk_prepare")
+        if not has_v or v_other.shape != (M, nkv * dv) or v_other.dtype != packed.dtype:
+            raise KernelError("qk_prepare: the other values must be [M, nkv * dv] in the packed dtype")
+        _opt_f32(blend, 1, "qk_prepare (blend)")
+        if blend is None:
+            raise KernelError("qk_prepare: blending values needs the blend's weight")
+    writes = kcache is not None
+    page_size = 0
+    if writes:
+        if slots is None or slots.dtype != torch.int32 or slots.shape != (M,):
+            raise KernelError("qk_prepare: slots must be int32 [M]")
+        for c, size in ((kcache, d),) + (((vcache, dv),) if has_v else ()):
+            if (c is None or c.dtype != packed.dtype or c.dim() != 4 or c.shape[1] != nkv or c.shape[3] != size
+                    or not c.is_contiguous()):
+                raise KernelError("qk_prepare: caches must be contiguous [pages, nkv, page_size, size] in the packed dtype")
+        page_size = int(kcache.shape[2])
+    lib = _lib("qk_prepare")
+    rc = lib.mi_qk_norm_rope_store(_ptr(packed), packed.stride(0), q_off, k_off, v_off if has_v else -1, M, nq, nkv, d,
+                                   dv, _ptr(q_gain), _ptr(k_gain), float(eps), int(rot), _ptr(positions), _ptr(freq),
+                                   float(q_scale), float(k_scale), _ptr(v_other),
+                                   v_other.stride(0) if v_other is not None else 0, _ptr(blend), _ptr(slots),
+                                   _ptr(kcache), _ptr(vcache if has_v else None), page_size, 1 if writes else 0,
+                                   _code(packed.dtype), _stream())
     _finish(lib, rc, "qk_prepare")
 
 
@@ -1781,12 +1938,13 @@ def _rows_attention_plan(ctx, nq: int, nkv: int, d: int, dv: int, values_in_keys
 
 def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: int, d: int, dv: int, scale: float, *,
                   window: int = 0, sinks: torch.Tensor | None = None, slopes: torch.Tensor | None = None,
-                  values_in_keys: bool = False) -> None:
+                  values_in_keys: bool = False, chunk: int = 0) -> None:
     """``attention_kv`` with the extras of the CUDA-core kernel: ``sinks`` (fp32 ``[nq]``: a score per
     head that joins the softmax's denominator without a key or a value), ``slopes`` (fp32 ``[nq]``:
     the scaled score of a key ``dist`` positions back is lowered by ``slope * dist``) and
     ``values_in_keys`` (the cache layer has keys only; a key's value is the first ``dv`` numbers of its
-    own row).  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 prompt portions
+    own row); ``chunk`` > 0: a query at position ``p`` sees only the keys of its own chunk of positions,
+    ``j >= (p // chunk) * chunk``.  fp32 scores, weights and sums for float32 and bfloat16 alike.  bfloat16 prompt portions
     with keys and values of one size that attention_tc.cu takes run on tcgen05; other bfloat16 steps with sizes that
     attention_rows.cu takes (``rows_attention_supported``) and tiles planned for it runs on tensor
     cores (weights rounded to bfloat16 for the second product); everything else on CUDA cores."""
@@ -1808,7 +1966,7 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     bt = group.block_table
     # prompt portions of heads that the tcgen05 prefill kernel takes (keys and values of 64 or 128) go there
     if (q.dtype == torch.bfloat16 and not values_in_keys and d == dv and not getattr(ctx, "decode_only", False)
-            and USE_TC_PREFILL and scale > 0 and prefill_tc_supported(nq, nkv, d, group.page_size)
+            and not chunk and USE_TC_PREFILL and scale > 0 and prefill_tc_supported(nq, nkv, d, group.page_size)
             and prefill_tc_tile_tokens(nq // nkv) in ctx.tiles and out.is_contiguous()
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
             and kc.data_ptr() % 128 == 0 and vc.data_ptr() % 128 == 0):
@@ -1818,7 +1976,8 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
                              tile_req, tile_tok0, n_tiles, tt, nq, nkv, d, scale, int(window),
                              table_rows=group.table_rows, sinks=sinks, slopes=slopes)
         return
-    if (q.dtype == torch.bfloat16 and not window and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
+    if (q.dtype == torch.bfloat16 and not window and not chunk
+            and rows_attention_supported(nq, nkv, d, dv, values_in_keys)
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
             and rows_attention_tile_tokens(nq // nkv, 16) in ctx.tiles):
         rows, tt, splits, stages = _rows_attention_plan(ctx, nq, nkv, d, dv, values_in_keys, q.device)
@@ -1842,10 +2001,10 @@ def attention_ext(q: torch.Tensor, out: torch.Tensor, cache, ctx, nq: int, nkv: 
     lib = _lib("attention_generic")
     if lib.mi_attention_generic_tile_tokens() != ATTENTION_TILE_TOKENS:
         raise KernelError("attention: the kernel's tile size differs from ATTENTION_TILE_TOKENS")
-    rc = lib.mi_attention_generic_ext(
+    rc = lib.mi_attention_generic_masked(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kc), _ptr(vc), _ptr(bt), bt.stride(0),
         _ptr(group.table_rows), int(group.page_size), _ptr(ctx.q_start), _ptr(ctx.q_len), _ptr(ctx.kv_len),
-        _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, d, dv, float(scale), int(window),
+        _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), nq, nkv, d, dv, float(scale), int(window), int(chunk),
         _ptr(sinks), _ptr(slopes), 1 if values_in_keys else 0, _code(q.dtype), _stream())
     _finish(lib, rc, "attention")
 

@@ -22,6 +22,15 @@
 //                           with i + rot/2; (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = p * freq[i];
 //                           the angle is computed and reduced to [-pi, pi] in double precision, its sine
 //                           and cosine in fp32.
+//   mi_qk_norm_rope_store   queries and keys get an RMS norm over the head with one gain shared by the heads
+//                           (optional), then the rotation of the half layout on their first `rot` dimensions
+//                           (angles as above), then a factor each (q_scale, k_scale); both are written back
+//                           in place and k goes to its cache page.  The values (optional: v_off < 0 means the
+//                           mixer has none here) may be blended with another layer's values of the same
+//                           tokens, v <- (1 - lam) v + lam v_other with lam read from device memory; they are
+//                           written back in place as well (a later layer may ask for them) and go to the
+//                           value pages.  Without pages nothing is stored: a mixer that keeps a state instead
+//                           of keys uses the kernel for the rotation alone.
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
@@ -214,5 +223,121 @@ extern "C" int mi_latent_prepare(const void* packed, int stride, int q_off, int 
               (bf16*)kcache, page_size, writes);
   else
     MI_REFUSE("latent_prepare: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+
+#define ROPE_MAX_D 1024
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_off, int v_off, int nq, int nkv, int d,
+                          int dv, const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                          int rot, const int* __restrict__ positions, const double* __restrict__ freq, float q_scale,
+                          float k_scale, const T* __restrict__ v_other, int v_other_stride,
+                          const float* __restrict__ lam_ptr, const int* __restrict__ slots, T* __restrict__ kcache,
+                          T* __restrict__ vcache, int page_size, int writes) {
+  mi_pdl_enter();
+  extern __shared__ float rope_sm[];
+  const int half = rot >> 1;
+  float* sn = rope_sm;                 // [half]
+  float* cs = sn + half;               // [half]
+  float* buf = cs + half;              // [warps][d] a head's values after the norm
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (half > 0) {
+    const double pos = (double)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      double a = pos * freq[i];
+      a -= 6.283185307179586476925 * rint(a * 0.15915494309189533577);
+      float s, c;
+      sincosf((float)a, &s, &c);
+      sn[i] = s;
+      cs[i] = c;
+    }
+  }
+  __syncthreads();
+  T* row = packed + (size_t)t * stride;
+  constexpr int EPC = 16 / (int)sizeof(T);
+  const int slot = writes ? slots[t] : 0;
+  const int page = slot / page_size, offset = slot - page * page_size;
+  const int mk = mi_swizzle_mask_rows(d, (int)sizeof(T)), mv = mi_swizzle_mask_rows(dv, (int)sizeof(T));
+  const int n_v = v_off >= 0 ? nkv : 0;
+  const float lam = lam_ptr ? *lam_ptr : 0.f;
+  float* mine = buf + (size_t)warp * d;
+  for (int h = blockIdx.y * nwarps + warp; h < nq + nkv + n_v; h += gridDim.y * nwarps) {
+    if (h >= nq + nkv) {               // values
+      const int kvh = h - nq - nkv;
+      T* src = row + v_off + kvh * dv;
+      T* dst = writes ? vcache + ((size_t)(page * nkv + kvh) * page_size + offset) * dv : nullptr;
+      const T* other = v_other ? v_other + (size_t)t * v_other_stride + kvh * dv : nullptr;
+      for (int k = lane; k < dv; k += 32) {
+        T y = src[k];
+        if (other) {
+          y = mi_from_float<T>((1.f - lam) * mi_to_float(y) + lam * mi_to_float(other[k]));
+          src[k] = y;
+        }
+        if (dst) dst[mi_swizzled(k, offset, mv, EPC)] = y;
+      }
+      continue;
+    }
+    const bool is_q = h < nq;
+    const int hh = is_q ? h : h - nq;
+    T* x = row + (is_q ? q_off : k_off) + hh * d;
+    const float* gain = is_q ? q_gain : k_gain;
+    const float post = is_q ? q_scale : k_scale;
+    float ss = 0.f;
+    for (int k = lane; k < d; k += 32) {
+      const float v = mi_to_float(x[k]);
+      mine[k] = v;
+      ss += v * v;
+    }
+    if (gain) {
+      ss = mi_warp_sum(ss);
+      const float mult = 1.f / sqrtf(ss / (float)d + eps);
+      for (int k = lane; k < d; k += 32) mine[k] = mine[k] * mult * gain[k];
+    }
+    __syncwarp();
+    T* kdst = (!is_q && writes) ? kcache + ((size_t)(page * nkv + hh) * page_size + offset) * d : nullptr;
+    for (int k = lane; k < d; k += 32) {
+      float y = mine[k];
+      if (k < rot) {
+        const int i = k < half ? k : k - half;
+        float y1, y2;
+        mi_rotate(mine[i], mine[i + half], sn[i], cs[i], y1, y2);
+        y = k < half ? y1 : y2;
+      }
+      const T out = mi_from_float<T>(y * post);
+      x[k] = out;
+      if (kdst) kdst[mi_swizzled(k, offset, mk, EPC)] = out;
+    }
+    __syncwarp();                      // the warp's buffer is free for its next head
+  }
+}
+
+extern "C" int mi_qk_norm_rope_store(void* packed, int stride, int q_off, int k_off, int v_off, int M, int nq, int nkv,
+                                     int d, int dv, const float* q_gain, const float* k_gain, float eps, int rot,
+                                     const int* positions, const double* freq, float q_scale, float k_scale,
+                                     const void* v_other, int v_other_stride, const float* lam, const int* slots,
+                                     void* kcache, void* vcache, int page_size, int writes, int dtype,
+                                     cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (d <= 0 || d > ROPE_MAX_D || dv < 0) MI_REFUSE("qk_prepare: head size %d must lie in [1, %d]", d, ROPE_MAX_D);
+  if (rot < 0 || rot > d || (rot & 1)) MI_REFUSE("qk_prepare: %d rotated dimensions of %d", rot, d);
+  if (rot > 0 && (!positions || !freq)) MI_REFUSE("qk_prepare: a rotation needs positions and frequencies");
+  if (v_other && !lam) MI_REFUSE("qk_prepare: blending values needs the blend's weight");
+  if (writes && (!slots || !kcache || page_size <= 0 || (v_off >= 0 && !vcache)))
+    MI_REFUSE("qk_prepare: a cache write needs slots and pages");
+  const int n_heads = nq + nkv + (v_off >= 0 ? nkv : 0);
+  const dim3 grid((unsigned)M, (unsigned)((n_heads + 3) / 4 < 64 ? (n_heads + 3) / 4 : 64));
+  const size_t smem = ((size_t)rot + 4 * (size_t)d) * sizeof(float);
+#define MI_GO(T)                                                                                                       \
+  MI_LAUNCH((qk_norm_rope_store_kernel<T>), grid, 128, smem, stream, (T*)packed, stride, q_off, k_off, v_off, nq, nkv, \
+            d, dv, q_gain, k_gain, eps, rot, positions, freq, q_scale, k_scale, (const T*)v_other, v_other_stride,    \
+            lam, slots, (T*)kcache, (T*)vcache, page_size, writes)
+  if (dtype == MI_DTYPE_F32) MI_GO(float);
+  else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
+  else MI_REFUSE("qk_prepare: unknown dtype %d", dtype);
+#undef MI_GO
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -8,13 +8,18 @@
 //
 //   mi_causal_conv     per channel: out[t] = b + sum_j w[j] * in[t - (taps-1-j)], in = x + x_bias,
 //                      with the taps-1 inputs before the portion taken from the state (zeros before
-//                      the start of a sequence).  Does not change the state.
+//                      the start of a sequence); optionally SiLU of the result.  Does not change the state.
 //   mi_rglru_scan      the real-gated linear recurrent unit:
 //                        r = sigmoid(gr + br), i = sigmoid(gi + bi), log a = -c * r * softplus(lam),
 //                        S = a S + sqrt(1 - a^2) * i * u;   out = T(S * gelu_tanh(y + by))
 //                      and, for the convolution in front of it, the new last taps-1 inputs.
 //   mi_gla_scan        gated linear attention, per head: S = diag(alpha) S + k v^T, o = S^T (q * qscale),
-//                      alpha = sigmoid(z + bz)^(1/tau).
+//                      alpha = sigmoid(z + bz)^(1/tau), or one fixed decay per head (head_decay).
+//   mi_delta_scan      the gated delta rule with a decay per key channel, per head:
+//                        S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                      with q and k made unit vectors per head first (q also times q_scale),
+//                      g = exp(-exp(A_log) * softplus(z + dt_bias)), beta = sigmoid(b); and, for the
+//                      convolution in front of it, the new last taps-1 inputs.
 //   mi_headnorm_gate   out = T(o / sqrt(mean_head(o^2) + eps) * w * act(g) * scale) per head of dv.
 #include "common.cuh"
 
@@ -32,7 +37,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int x_stride, const 
                                    const float* __restrict__ state, long long state_stride,
                                    const int* __restrict__ q_start, const int* __restrict__ q_len,
                                    const int* __restrict__ state_slot, T* __restrict__ out, int out_stride,
-                                   int C, int taps, int tile) {
+                                   int C, int taps, int tile, int act) {
   mi_pdl_enter();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int req = blockIdx.z;
@@ -57,6 +62,7 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int x_stride, const 
         acc = fmaf(wv[j], v, acc);
       }
     }
+    if (act == 1) acc = acc / (1.f + expf(-acc));   // SiLU
     out[(size_t)(row0 + t) * out_stride + c] = mi_from_float<T>(acc);
   }
 }
@@ -64,18 +70,19 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int x_stride, const 
 extern "C" int mi_causal_conv(const void* x, int x_stride, const float* x_bias, const float* w, const float* b,
                               const float* state, long long state_stride, const int* q_start, const int* q_len,
                               const int* state_slot, void* out, int out_stride, int n_requests, int max_q_len,
-                              int C, int taps, int dtype, cudaStream_t stream) {
+                              int C, int taps, int act, int dtype, cudaStream_t stream) {
   if (n_requests <= 0 || max_q_len <= 0) return 0;
+  if (act != 0 && act != 1) MI_REFUSE("causal_conv: unknown activation %d", act);
   if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("causal_conv: %d taps (1 to %d are taken)", taps, MAX_TAPS);
   const int tile = 16;
   dim3 grid((C + 127) / 128, (max_q_len + tile - 1) / tile, n_requests);
   if (grid.y > 65535 || grid.z > 65535) MI_REFUSE("causal_conv: too many tiles for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((causal_conv_kernel<float>), grid, 128, 0, stream, (const float*)x, x_stride, x_bias, w, b, state,
-              state_stride, q_start, q_len, state_slot, (float*)out, out_stride, C, taps, tile);
+              state_stride, q_start, q_len, state_slot, (float*)out, out_stride, C, taps, tile, act);
   else if (dtype == MI_DTYPE_BF16)
     MI_LAUNCH((causal_conv_kernel<bf16>), grid, 128, 0, stream, (const bf16*)x, x_stride, x_bias, w, b, state,
-              state_stride, q_start, q_len, state_slot, (bf16*)out, out_stride, C, taps, tile);
+              state_stride, q_start, q_len, state_slot, (bf16*)out, out_stride, C, taps, tile, act);
   else
     MI_REFUSE("causal_conv: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();
@@ -307,7 +314,8 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
                                 const int* __restrict__ state_slot, float* __restrict__ o, int o_stride,
                                 int heads, int dk, int dv, int pass, int chunk_len, int n_chunks,
-                                float* __restrict__ scratch) {
+                                float* __restrict__ scratch, const float* __restrict__ head_decay) {
+  // head_decay [heads]: one fixed decay per head in the place of alpha (z is then not read).
   // pass 0: the whole portion, from and into the state.  Long portions run as chunks side by side:
   // pass 1 folds every chunk into (A, B) with S_end = diag(A) S_begin + B (and saves the state the
   // portion starts from), pass 2 walks the chunks before its own to get S_begin and then its own
@@ -369,7 +377,7 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
         const size_t m = (size_t)(row0 + t0 + l);
         pq[i] = mi_to_float(q[m * stride + head * dk + kk]);
         pk[i] = mi_to_float(k[m * stride + head * dk + kk]);
-        pz[i] = z[m * z_stride + head * dk + kk];
+        pz[i] = head_decay ? 0.f : z[m * z_stride + head * dk + kk];
       }
     }
 #pragma unroll
@@ -393,7 +401,8 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
         qs[idx] = pq[i] * q_scale;
         ks[idx] = pk[i];
         const float zz = pz[i] + (z_bias ? z_bias[head * dk + kk] : 0.f);
-        as[idx] = expf(-mi_softplus(-zz) * inv_tau);     // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
+        as[idx] = head_decay ? head_decay[head]
+                             : expf(-mi_softplus(-zz) * inv_tau);     // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
       }
     }
 #pragma unroll
@@ -447,8 +456,9 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
                            const float* z_bias, float inv_tau, float q_scale, float* state, long long state_stride,
                            const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
                            int n_requests, int heads, int dk, int dv, float* scratch, int n_chunks, int chunk_len,
-                           int dtype, cudaStream_t stream) {
+                           const float* head_decay, int dtype, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
+  if (!z && !head_decay) MI_REFUSE("gla: neither decays per channel nor decays per head");
   if (n_chunks < 1 || (n_chunks > 1 && (!scratch || chunk_len <= 0))) MI_REFUSE("gla: chunks need scratch memory");
   if ((long long)n_requests * n_chunks > 65535) MI_REFUSE("gla: too many chunks for one launch");
   if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("gla: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
@@ -466,11 +476,208 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
     for (int pass = n_chunks > 1 ? 1 : 0; pass <= (n_chunks > 1 ? 2 : 0); ++pass)                         \
       MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride, \
                 z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, \
-                dk, dv, pass, chunk_len, n_chunks, scratch);                                               \
+                dk, dv, pass, chunk_len, n_chunks, scratch, head_decay);                                   \
   } while (0)
   if (dtype == MI_DTYPE_F32) MI_GO(float);
   else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
   else MI_REFUSE("gla: unknown dtype %d", dtype);
+#undef MI_GO
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// gated delta rule.  The columns of a head's state S [dk, dv] evolve independently under the same
+// transition, so a warp owns DELTA_NC columns: lane l keeps rows l, l + 32, ... of each in registers.
+// Per token and column: sg = g * s; r = sg . k; p = sg . q; u = beta (v - r); s = sg + k u;
+// o = p + u (k . q), which is S^T q after the write.  The two dot products of all the warp's columns
+// are reduced over the lanes together.  Tokens are staged in groups of DELTA_L: the block's warps make
+// q and k unit vectors, compute g, beta and k . q, and leave them in shared memory for the walk.
+// A block has DELTA_W warps, so it owns DELTA_W * DELTA_NC value columns of one head of one request.
+// state row of a request: [taps-1][C] convolution inputs (oldest first), then S [heads][dk][dv].
+// ------------------------------------------------------------------------------------------
+#define DELTA_L 16
+#define DELTA_NC 4
+#define DELTA_W 8
+#define DELTA_COLS (DELTA_NC * DELTA_W)
+
+template <typename T, int R>
+__global__ void __launch_bounds__(32 * DELTA_W)
+delta_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int stride,
+                  const float* __restrict__ z, int z_stride, const float* __restrict__ dt_bias,
+                  const float* __restrict__ a_log, const T* __restrict__ b, int b_stride, float q_scale,
+                  float unit_eps, float* __restrict__ state, long long state_stride, long long s_off,
+                  const int* __restrict__ q_start, const int* __restrict__ q_len,
+                  const int* __restrict__ state_slot, float* __restrict__ o, int o_stride, int heads, int kv_heads,
+                  int dk, int dv, const T* __restrict__ xin, int xin_stride, int C, int taps) {
+  mi_pdl_enter();
+  extern __shared__ float dsm[];
+  float* ks = dsm;                       // [DELTA_L][dk]
+  float* qs = ks + DELTA_L * dk;         // [DELTA_L][dk]
+  float* gs = qs + DELTA_L * dk;         // [DELTA_L][dk]
+  float* vs = gs + DELTA_L * dk;         // [DELTA_L][DELTA_COLS]
+  float* bs = vs + DELTA_L * DELTA_COLS; // [DELTA_L] beta
+  float* kqs = bs + DELTA_L;             // [DELTA_L] k . q
+  const int lane = threadIdx.x, warp = threadIdx.y, tid = warp * 32 + lane;
+  const int head = blockIdx.y, req = blockIdx.z;
+  const int kvh = head / (heads / kv_heads);
+  const int len = q_len[req], row0 = q_start[req];
+  float* st = state + (size_t)state_slot[req] * state_stride;
+  float* S = st + s_off + (size_t)head * dk * dv;
+  const int j0 = blockIdx.x * DELTA_COLS + warp * DELTA_NC;
+  const float A = expf(a_log[head]);
+  float s[R][DELTA_NC];
+#pragma unroll
+  for (int i = 0; i < R; ++i)
+#pragma unroll
+    for (int c = 0; c < DELTA_NC; ++c) {
+      const int kk = lane + 32 * i, j = j0 + c;
+      s[i][c] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
+    }
+  for (int t0 = 0; t0 < len; t0 += DELTA_L) {
+    const int n = min(DELTA_L, len - t0);
+    __syncthreads();   // the group before is consumed
+    for (int l = warp; l < n; l += DELTA_W) {
+      const size_t m = (size_t)(row0 + t0 + l);
+      const T* kr = k + m * stride + kvh * dk;
+      const T* qr = q + m * stride + kvh * dk;
+      float kv_[R], qv_[R], ssk = 0.f, ssq = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int kk = lane + 32 * i;
+        kv_[i] = kk < dk ? mi_to_float(kr[kk]) : 0.f;
+        qv_[i] = kk < dk ? mi_to_float(qr[kk]) : 0.f;
+        ssk = fmaf(kv_[i], kv_[i], ssk);
+        ssq = fmaf(qv_[i], qv_[i], ssq);
+      }
+      ssk = mi_warp_sum(ssk);
+      ssq = mi_warp_sum(ssq);
+      const float mk = 1.f / sqrtf(ssk + unit_eps), mq = q_scale / sqrtf(ssq + unit_eps);
+      float kq = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int kk = lane + 32 * i;
+        if (kk < dk) {
+          const float kn = kv_[i] * mk, qn = qv_[i] * mq;
+          ks[l * dk + kk] = kn;
+          qs[l * dk + kk] = qn;
+          kq = fmaf(kn, qn, kq);
+          const float dt = mi_softplus(z[m * z_stride + head * dk + kk] + dt_bias[head * dk + kk]);
+          gs[l * dk + kk] = expf(-A * dt);
+        }
+      }
+      kq = mi_warp_sum(kq);
+      if (lane == 0) {
+        kqs[l] = kq;
+        bs[l] = mi_sigmoid(mi_to_float(b[m * b_stride + head]));
+      }
+      const int jj = blockIdx.x * DELTA_COLS + lane;
+      vs[l * DELTA_COLS + lane] = jj < dv ? mi_to_float(v[m * stride + head * dv + jj]) : 0.f;
+    }
+    __syncthreads();
+    for (int l = 0; l < n; ++l) {
+      float r[DELTA_NC], pq[DELTA_NC];
+#pragma unroll
+      for (int c = 0; c < DELTA_NC; ++c) r[c] = pq[c] = 0.f;
+      float kreg[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const int kk = lane + 32 * i;
+        const bool in = kk < dk;
+        const float g = in ? gs[l * dk + kk] : 1.f, qn = in ? qs[l * dk + kk] : 0.f;
+        kreg[i] = in ? ks[l * dk + kk] : 0.f;
+#pragma unroll
+        for (int c = 0; c < DELTA_NC; ++c) {
+          s[i][c] *= g;
+          r[c] = fmaf(s[i][c], kreg[i], r[c]);
+          pq[c] = fmaf(s[i][c], qn, pq[c]);
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+        for (int c = 0; c < DELTA_NC; ++c) {
+          r[c] += __shfl_xor_sync(0xffffffffu, r[c], off);
+          pq[c] += __shfl_xor_sync(0xffffffffu, pq[c], off);
+        }
+      const float beta = bs[l], kq = kqs[l];
+      float u[DELTA_NC];
+#pragma unroll
+      for (int c = 0; c < DELTA_NC; ++c) u[c] = beta * (vs[l * DELTA_COLS + warp * DELTA_NC + c] - r[c]);
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int c = 0; c < DELTA_NC; ++c) s[i][c] = fmaf(kreg[i], u[c], s[i][c]);
+      if (lane < DELTA_NC && j0 + lane < dv) {
+        float ov = 0.f;
+#pragma unroll
+        for (int c = 0; c < DELTA_NC; ++c)
+          if (c == lane) ov = fmaf(u[c], kq, pq[c]);
+        o[(size_t)(row0 + t0 + l) * o_stride + head * dv + j0 + lane] = ov;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < R; ++i)
+#pragma unroll
+    for (int c = 0; c < DELTA_NC; ++c) {
+      const int kk = lane + 32 * i, j = j0 + c;
+      if (kk < dk && j < dv) S[(size_t)kk * dv + j] = s[i][c];
+    }
+  // the convolution's next tail (one block per request does it): the last taps-1 of (old tail, this
+  // portion's inputs); the convolution itself ran before this kernel
+  if (taps > 1 && blockIdx.x == 0 && blockIdx.y == 0) {
+    for (int c = tid; c < C; c += 32 * DELTA_W) {
+      float keep[MAX_TAPS];
+#pragma unroll
+      for (int j = 0; j < MAX_TAPS - 1; ++j) {
+        if (j < taps - 1) {
+          const int src = len - (taps - 1) + j;
+          keep[j] = src >= 0 ? mi_to_float(xin[(size_t)(row0 + src) * xin_stride + c])
+                             : st[(size_t)(taps - 1 + src) * C + c];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < MAX_TAPS - 1; ++j)
+        if (j < taps - 1) st[(size_t)j * C + c] = keep[j];
+    }
+  }
+}
+
+extern "C" int mi_delta_scan(const void* q, const void* k, const void* v, int stride, const float* z, int z_stride,
+                             const float* dt_bias, const float* a_log, const void* b, int b_stride, float q_scale,
+                             float unit_eps, float* state, long long state_stride, long long s_off,
+                             const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
+                             int n_requests, int heads, int kv_heads, int dk, int dv, const void* xin, int xin_stride,
+                             int C, int taps, int dtype, cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("delta: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) MI_REFUSE("delta: %d heads cannot share %d key heads", heads, kv_heads);
+  if (heads > 65535 || n_requests > 65535) MI_REFUSE("delta: too many heads or requests for one launch");
+  if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("delta: %d taps (1 to %d are taken)", taps, MAX_TAPS);
+  dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, heads, n_requests), block(32, DELTA_W);
+  const size_t smem = ((size_t)3 * DELTA_L * dk + DELTA_L * DELTA_COLS + 2 * DELTA_L) * sizeof(float);
+#define MI_GO(T, R)                                                                                                  \
+  do {                                                                                                               \
+    auto kern = delta_scan_kernel<T, R>;                                                                             \
+    if (smem > 48 * 1024) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+    }                                                                                                                \
+    MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride, dt_bias,  \
+              a_log, (const T*)b, b_stride, q_scale, unit_eps, state, state_stride, s_off, q_start, q_len,          \
+              state_slot, o, o_stride, heads, kv_heads, dk, dv, (const T*)xin, xin_stride, C, taps);                 \
+  } while (0)
+#define MI_GO_R(T)                  \
+  do {                              \
+    if (dk <= 32) MI_GO(T, 1);      \
+    else if (dk <= 64) MI_GO(T, 2); \
+    else if (dk <= 128) MI_GO(T, 4);\
+    else MI_GO(T, 8);               \
+  } while (0)
+  if (dtype == MI_DTYPE_F32) MI_GO_R(float);
+  else if (dtype == MI_DTYPE_BF16) MI_GO_R(bf16);
+  else MI_REFUSE("delta: unknown dtype %d", dtype);
+#undef MI_GO_R
 #undef MI_GO
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -8,7 +8,8 @@
 //                        unit_norm, divided by sqrt(mean(x^2) + eps) over the head; q is written back
 //                        in place, k and v go to their cache pages (k of size d, v of size dv).
 //                        Angles, sines, cosines and the norm are fp32; each value is rounded once.
-//   mi_gate_mul          out[t, off + c] = T(x[t, c] * act(g[t, c]) * scale), act = sigmoid or SiLU.
+//   mi_gate_mul          out[t, c] = T(x[t, c] * act(g[t, c / per]) * scale), act = sigmoid or SiLU; per = 1: a
+//                        gate per element, per = a head's size: one gate per head.
 //
 // q, k, v and the gate are column ranges of one packed projection [tokens, stride].
 #include "common.cuh"
@@ -114,12 +115,12 @@ extern "C" int mi_rope_norm_store(void* qkv, int stride, int q_off, int k_off, i
 // act: 1 sigmoid, 2 SiLU
 template <typename T>
 __global__ void gate_mul_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ g, int g_stride,
-                                T* __restrict__ out, int out_stride, int M, int C, int act, float scale) {
+                                T* __restrict__ out, int out_stride, int M, int C, int act, float scale, int per) {
   mi_pdl_enter();
   const size_t n = (size_t)M * C;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / C), c = (int)(idx - (size_t)t * C);
-    const float gv = mi_to_float(g[(size_t)t * g_stride + c]);
+    const float gv = mi_to_float(g[(size_t)t * g_stride + c / per]);
     const float sg = 1.f / (1.f + expf(-gv));
     const float a = act == 2 ? gv * sg : sg;
     out[(size_t)t * out_stride + c] = mi_from_float<T>(mi_to_float(x[(size_t)t * x_stride + c]) * a * scale);
@@ -127,17 +128,18 @@ __global__ void gate_mul_kernel(const T* __restrict__ x, int x_stride, const T* 
 }
 
 extern "C" int mi_gate_mul(const void* x, int x_stride, const void* g, int g_stride, void* out, int out_stride,
-                           int M, int C, int act, float scale, int dtype, cudaStream_t stream) {
+                           int M, int C, int act, float scale, int per, int dtype, cudaStream_t stream) {
   if (M <= 0 || C <= 0) return 0;
+  if (per <= 0) MI_REFUSE("gate_mul: %d columns per gate", per);
   if (act != 1 && act != 2) MI_REFUSE("gate_mul: unknown activation %d", act);
   const size_t n = (size_t)M * C;
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((gate_mul_kernel<float>), blocks, 256, 0, stream, (const float*)x, x_stride, (const float*)g, g_stride,
-              (float*)out, out_stride, M, C, act, scale);
+              (float*)out, out_stride, M, C, act, scale, per);
   else if (dtype == MI_DTYPE_BF16)
     MI_LAUNCH((gate_mul_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)x, x_stride, (const bf16*)g, g_stride,
-              (bf16*)out, out_stride, M, C, act, scale);
+              (bf16*)out, out_stride, M, C, act, scale, per);
   else
     MI_REFUSE("gate_mul: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

@@ -7,6 +7,8 @@
 //                            portion's first token, the request's entry of last_token[] (per request
 //                            slot), which the block of that first token then replaces by the portion's
 //                            last token.
+//   mi_embedding_rmsnorm     stream[t, :] = x * rsqrt(mean(x^2) + eps) * gain with x = float(table[id_t, :]): an
+//                            embedding that is normalised before it becomes the fp32 stream.
 //   mi_add_rmsnorm_multi     r = stream_in[src] + (float(add1[src]) + float(add2[src])) + add32[src] + row_add
 //                            (fp32; every addend optional); stream_out[i] = r (if given; may be stream_in
 //                            when there is no gather); out[i] = T(r * rsqrt(mean(r^2) + eps) * gain).
@@ -186,5 +188,43 @@ extern "C" int mi_glu_mul_pairs(const void* gu, void* out, int M, int I, int act
     MI_LAUNCH((glu_mul_pairs_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, M, I, act);
   else
     MI_REFUSE("glu_mul: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+
+template <typename T>
+__global__ void embedding_rmsnorm_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                         const float* __restrict__ gain, float* __restrict__ out, int H, int V,
+                                         float eps) {
+  mi_pdl_enter();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * H;
+  if ((unsigned)id >= (unsigned)V) {    // the step function validates ids; this keeps a fault visible
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + (size_t)id * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = mi_to_float(src[i]);
+    ss += v * v;
+  }
+  const float mult = 1.f / sqrtf(mi_block_sum(ss, red) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = mi_to_float(src[i]) * mult * gain[i];
+}
+
+extern "C" int mi_embedding_rmsnorm(const void* table, const int* ids, const float* gain, float* out, int M, int H,
+                                    int V, float eps, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (H <= 0 || V <= 0) MI_REFUSE("embedding: bad sizes H=%d V=%d", H, V);
+  const int threads = H >= 1024 ? 256 : 128;
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((embedding_rmsnorm_kernel<float>), M, threads, 0, stream, (const float*)table, ids, gain, out, H, V, eps);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((embedding_rmsnorm_kernel<bf16>), M, threads, 0, stream, (const bf16*)table, ids, gain, out, H, V, eps);
+  else
+    MI_REFUSE("embedding: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -53,12 +53,15 @@ class KVNeed:
     """Per-token keys and values kept in pages: ``kv_heads * head_dim`` numbers each per
     token.  ``window``: only the last ``window`` positions are ever read (None: all).
     ``value_dim``: size of a value per head where it is not ``head_dim`` (keys keep ``head_dim``);
-    0: nothing is kept beside the keys (the mixer finds its values in them)."""
+    0: nothing is kept beside the keys (the mixer finds its values in them).
+    ``chunk``: a query reads only the keys of its own chunk of ``chunk`` positions (counted from
+    position 0), so whole chunks behind the sequence's end are never read again (None: no chunks)."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)

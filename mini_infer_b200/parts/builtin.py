@@ -228,17 +228,32 @@ class RotaryPosition(Position):
     and cosine are fp32 and computed in the kernel; each rotated value is rounded once.
 
     params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default ``head_dim``),
-    optional ``scaling`` (the llama3 mapping).
+    optional ``scaling`` (the llama3 mapping), optional ``span`` (``"head"``, the default: dimension
+    ``i`` turns with ``theta^(-2i / head_dim)``; ``"rotated"``: with ``theta^(-2i / rotary_dim)``).
+
+    A mixer whose own kernel rotates reads ``rotary_dim`` and ``freq64`` (the frequencies in float64:
+    such a kernel forms the angle in double precision).
     """
 
     def bind(self, tensors, dtype, device):
         d = int(self.param("head_dim"))
         self.rotary_dim = int(self.spec.params.get("rotary_dim") or d)
+        span = self.spec.params.get("span", "head")
+        if span not in ("head", "rotated"):
+            raise ValueError(f"unknown span {span!r} of the rotation's frequencies: 'head' or 'rotated'")
+        if self.rotary_dim % 2 or not 0 < self.rotary_dim <= d:
+            raise ValueError(f"{self.rotary_dim} rotated dimensions of a head of {d}")
+        over = d if span == "head" else self.rotary_dim
         self.inv_freq = rotary_inv_freq(
-            d, float(self.param("theta")), self.rotary_dim, self.spec.params.get("scaling")
+            over, float(self.param("theta")), self.rotary_dim, self.spec.params.get("scaling")
         ).to(device)
+        if self.spec.params.get("scaling") is None:
+            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            self.freq64 = (float(self.param("theta")) ** (-2.0 * i / over)).to(device)
+        else:
+            self.freq64 = self.inv_freq.to(torch.float64)
         # layers with the same frequencies share one table per step
-        self._table_key = (d, self.rotary_dim, float(self.param("theta")), repr(self.spec.params.get("scaling")))
+        self._table_key = (d, self.rotary_dim, float(self.param("theta")), repr(self.spec.params.get("scaling")), span)
 
     def encode(self, qkv, nq, nkv, head_dim, ctx):
         ops.rope_write(qkv, nq, nkv, head_dim, positions=ctx.positions, inv_freq=self.inv_freq,
@@ -421,23 +436,61 @@ class SwiGLU(FeedForward):
         return self.down_proj(h) if into is None else self.down_proj.into_stream(h, into)
 
 
+class ClampedGLU(FeedForward):
+    """``down(g' * sigmoid(alpha g') * (u' + up_offset))`` with ``g' = min(gate(x), limit)`` and
+    ``u' = clamp(up(x), -limit, limit)``, no biases: the dense form of the routed experts' clamped
+    activation.  gate and up are one merged product (gate rows, then up rows).
+
+    params: ``hidden_size``, ``intermediate_size``, ``limit``, optional ``alpha`` (default 1.702),
+    ``up_offset`` (default 1).  tensors: ``gate``, ``up``, ``down``.
+    """
+
+    def param_decls(self):
+        H, I = int(self.param("hidden_size")), int(self.param("intermediate_size"))
+        return {"gate": ParamDecl((I, H)), "up": ParamDecl((I, H)), "down": ParamDecl((H, I))}
+
+    def bind(self, tensors, dtype, device):
+        self.limit = float(self.param("limit"))
+        self.alpha = float(self.spec.params.get("alpha", 1.702))
+        self.up_offset = float(self.spec.params.get("up_offset", 1.0))
+        self.gate_up = Linear(torch.cat([_as_compute(tensors["gate"], dtype), _as_compute(tensors["up"], dtype)],
+                                        dim=0).contiguous())
+        self.down = Linear(_as_compute(tensors["down"], dtype).contiguous())
+
+    def forward(self, x, ctx):
+        return self.down(ops.clamped_glu(self.gate_up(x), self.limit, self.alpha, self.up_offset))
+
+
 # ----------------------------------------------------------------------------- embedding / head
 
 
 class TokenEmbedding(Part):
     """``h0 = E[token]`` (reference ``models/llama/llama.py:104,159``), or with ``scale``
-    ``h0 = float(E[token]) * scale``, which is then the fp32 residual stream itself.
+    ``h0 = float(E[token]) * scale``, or with ``norm_eps`` ``h0 = x / sqrt(mean(x^2) + norm_eps) * w``
+    (``x = float(E[token])``, an RMS norm of the embedding's own); the latter two are then the fp32
+    residual stream itself.
 
-    params: ``vocab_size``, ``hidden_size``, optional ``scale``.  tensors: ``weight [vocab, hidden]``.
+    params: ``vocab_size``, ``hidden_size``, optional ``scale``, optional ``norm_eps``.
+    tensors: ``weight [vocab, hidden]`` and, with ``norm_eps``, ``norm [hidden]``.
     """
 
     def param_decls(self):
-        return {"weight": ParamDecl((int(self.param("vocab_size")), int(self.param("hidden_size"))))}
+        decls = {"weight": ParamDecl((int(self.param("vocab_size")), int(self.param("hidden_size"))))}
+        if self.spec.params.get("norm_eps") is not None:
+            if self.spec.params.get("scale") is not None:
+                raise ValueError("an embedding is scaled or normalised, not both")
+            decls["norm"] = ParamDecl((int(self.param("hidden_size")),), "gain")
+        return decls
 
     def bind(self, tensors, dtype, device):
         self.weight = _as_compute(tensors["weight"], dtype).contiguous()
+        self.norm_gain = None
+        if self.spec.params.get("norm_eps") is not None:
+            self.norm_gain = tensors["norm"].to(torch.float32).contiguous()
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.norm_gain is not None:
+            return ops.embedding_rmsnorm(self.weight, ctx.token_ids, self.norm_gain, float(self.spec.params["norm_eps"]))
         scale = self.spec.params.get("scale")
         if scale is not None:
             return ops.embedding_scaled(self.weight, ctx.token_ids, float(scale))
@@ -485,6 +538,8 @@ class PreNormBlock(Arrangement):
     product adds its result to the stream itself and the product after the norm finishes the
     norm in its epilogue, so that the norm launches nothing: within the block for the second
     norm, and across blocks when the layer that follows gave its ``entry``.
+
+    A layer without a feed-forward (``no_feed_forward``) is ``h += mixer(norm1(h))`` alone.
     """
 
     def entry(self):
@@ -501,6 +556,8 @@ class PreNormBlock(Arrangement):
     def forward(self, x, residual, ctx, cache, following=None):
         n = ctx.n_tokens
         a, residual = self.mixer_norm.forward(x, residual)
+        if isinstance(self.feed_forward, NoFeedForward):
+            return self.mixer.forward(a, ctx, cache, self.position), residual
         sink = self._sink(self.mixer, self.feed_forward_norm, self.feed_forward, residual, n)
         if sink is None:
             h = self.mixer.forward(a, ctx, cache, self.position)
@@ -563,6 +620,7 @@ register_position("rotary", RotaryPosition, replace=True)
 register_mixer("gqa_attention", GroupedQueryAttention, replace=True)
 register_feed_forward("swiglu", SwiGLU, replace=True)
 register_feed_forward("gated_mlp", SwiGLU, replace=True)
+register_feed_forward("clamped_glu_mlp", ClampedGLU, replace=True)
 register_embedding("token_embedding", TokenEmbedding, replace=True)
 register_head("linear_head", OutputHead, replace=True)
 register_arrangement("prenorm", PreNormBlock, replace=True)

@@ -13,13 +13,19 @@ from .builtin import Linear, _as_compute
 
 class RoutedExperts(FeedForward):
     """Router logits ``z = W_r h`` in fp32; a token's ``top`` experts are those with the largest
-    logits and their weights the softmax over those logits alone; the output is the weighted sum of
-    their outputs, plus the shared expert's where there is one.  An expert is
+    logits and their weights the softmax over those logits alone (``scores`` ``"chosen"``, the
+    default), or their scores under the softmax over all experts, divided by the sum of these
+    (+ 1e-20) and multiplied by ``route_scale`` (``scores`` ``"all"``).  With ``groups`` > 1 the experts
+    form that many equal groups of neighbours, a group counts as its best expert, and only experts of
+    the ``keep_groups`` best groups can be chosen.  The output is the weighted sum of the chosen
+    experts' outputs, plus the shared expert's where there is one.  An expert is
     ``W_down (g' * sigmoid(alpha g') * (u' + 1))`` with ``g' = min(W_gate h, limit)`` and
-    ``u' = clamp(W_up h, -limit, limit)``, no biases.
+    ``u' = clamp(W_up h, -limit, limit)`` (``activation`` ``"clamped"``, the default), or
+    ``W_down (silu(W_gate h) * W_up h)`` (``"silu"``), no biases.
 
-    params: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit``, optional ``alpha``
-    (default 1.702), ``shared_ff`` (0 or absent: no shared expert), ``shared_limit``.
+    params: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit`` (with the clamped activation),
+    optional ``alpha`` (default 1.702), ``shared_ff`` (0 or absent: no shared expert), ``shared_limit``,
+    ``activation``, ``scores``, ``route_scale`` (default 1), ``groups`` and ``keep_groups``.
     tensors: ``router``, ``e{i}.gate``, ``e{i}.up``, ``e{i}.down`` and, with a shared expert,
     ``shared.gate``, ``shared.up``, ``shared.down``.
     """
@@ -30,12 +36,27 @@ class RoutedExperts(FeedForward):
         self.hidden = int(self.param("hidden_size"))
         self.experts, self.top = int(self.param("experts")), int(self.param("top"))
         self.ff = int(self.param("expert_ff"))
-        self.limit = float(self.param("limit"))
-        self.alpha = float(g("alpha", 1.702))
+        self.activation = str(g("activation", "clamped"))
+        if self.activation == "clamped":
+            self.limit, self.alpha, self.up_offset = float(self.param("limit")), float(g("alpha", 1.702)), 1.0
+        elif self.activation == "silu":     # the clamped form without a limit, with alpha 1 and no offset
+            self.limit, self.alpha, self.up_offset = float("inf"), 1.0, 0.0
+        else:
+            raise ValueError(f"unknown activation {self.activation!r} of the experts: 'clamped' or 'silu'")
+        self.scores = str(g("scores", "chosen"))
+        if self.scores not in ("chosen", "all"):
+            raise ValueError(f"unknown scores {self.scores!r} of the router: 'chosen' or 'all'")
+        self.route_scale = float(g("route_scale", 1.0))
+        self.groups, self.keep_groups = int(g("groups") or 0), int(g("keep_groups") or 0)
         self.shared_ff = int(g("shared_ff") or 0)
         self.shared_limit = float(g("shared_limit", self.limit))
         if not 0 < self.top <= self.experts:
             raise ValueError(f"{self.top} of {self.experts} experts per token")
+        if self.groups > 1:
+            if self.experts % self.groups or not 0 < self.keep_groups <= self.groups:
+                raise ValueError(f"{self.experts} experts in {self.groups} groups of which {self.keep_groups} are kept")
+            if self.keep_groups * (self.experts // self.groups) < self.top:
+                raise ValueError(f"{self.keep_groups} groups of {self.experts // self.groups} experts cannot give {self.top}")
 
     def param_decls(self):
         H, ff = self.hidden, self.ff
@@ -66,9 +87,12 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         shared = None
         if self.shared_in is not None:
-            shared = self.shared_out(ops.clamped_glu(self.shared_in(x), self.shared_limit, self.alpha))
-        ids, weights = ops.moe_route(x, self.router, self.top)
-        return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit, self.alpha, shared)
+            limit = self.shared_limit if self.activation == "clamped" else self.limit
+            shared = self.shared_out(ops.clamped_glu(self.shared_in(x), limit, self.alpha, self.up_offset))
+        ids, weights = ops.moe_route(x, self.router, self.top, all_scores=self.scores == "all", groups=self.groups,
+                                     keep_groups=self.keep_groups, scale=self.route_scale)
+        return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit, self.alpha, shared,
+                               up_offset=self.up_offset)
 
 
 register_feed_forward("routed_experts", RoutedExperts, replace=True)

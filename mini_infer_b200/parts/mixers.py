@@ -1,6 +1,8 @@
 """Mixers beyond plain grouped-query attention: a sliding-window attention with unit-norm queries
-and keys and gated heads, two recurrent mixers that keep a state of fixed size per request (the
-real-gated linear recurrent unit and gated linear attention), and a mixer that runs two of them
+and keys and gated heads, an attention over chunks of positions with normed queries and keys,
+blended values and a gate per head, four recurrent mixers that keep a state of fixed size per
+request (the real-gated linear recurrent unit, gated linear attention, retention with a fixed decay
+per head, and the gated delta rule with a decay per key channel), and a mixer that runs two of them
 side by side on the same input.
 
 They share one shape (``ProjectedMixer``): everything a mixer projects from its input is one
@@ -16,7 +18,7 @@ import torch
 
 from ..csrc import ops
 from .base import KVNeed, LayerCache, Mixer, ParamDecl, PlanNeeds, StateNeed, StepContext, build_part, register_mixer
-from .builtin import InterleavedRotary, Linear, _as_compute
+from .builtin import InterleavedRotary, Linear, RotaryPosition, _as_compute
 from .spec import PartSpec
 
 
@@ -153,6 +155,120 @@ class GatedWindowAttention(ProjectedMixer):
             raise ValueError("an ungated attention cannot scale its output")
 
 
+
+# ----------------------------------------------------------------------------- attention over chunks of positions
+
+
+def _half_rotation(position, d: int):
+    """``(rotated dimensions, float64 frequencies)`` of a mixer whose own kernel rotates in the half layout."""
+    if position is None:
+        return 0, None
+    if not isinstance(position, RotaryPosition):
+        raise ValueError("this mixer takes a rotary encoding of the half layout or none")
+    if position.rotary_dim > d:
+        raise ValueError(f"{position.rotary_dim} rotated dimensions of a head of {d}")
+    return position.rotary_dim, position.freq64
+
+
+class ChunkAttention(ProjectedMixer):
+    """Softmax attention with ``num_heads`` query heads sharing ``num_kv_heads`` key/value heads, keys of
+    ``head_dim`` and values of ``value_dim`` per head, in which position ``i`` sees ``j <= i`` of its own
+    chunk of positions only (``i // chunk == j // chunk``, chunks counted from position 0; no ``chunk``:
+    all of the past).  Queries and keys get an RMS norm over the head with a gain shared by the heads
+    (``qk_norm``), then the position encoding (a ``RotaryPosition``, half layout, or none); the score is
+    ``q . k * scale``.  With ``value_blend`` the values of every such layer of a model but the first to
+    run become ``(1 - lam) v + lam v_first`` (``lam`` the layer's ``vmix``, ``v_first`` the first such
+    layer's values of the same token); the blended values are what is cached.  With ``head_gate`` head
+    ``h``'s output is multiplied by ``sigmoid(W_g x)_h``, one number per head.  Scores, weights and sums
+    are fp32 for either dtype.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``; optional ``value_dim``
+    (default ``head_dim``), ``chunk``, ``qk_norm`` (default False) with ``eps``, ``value_blend`` and
+    ``head_gate`` (default False).
+    tensors: ``q``, ``k``, ``v``, ``o`` and, as asked, ``q.norm``, ``k.norm``, ``vmix``, ``g``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = self.spec.params.get
+        self.hidden = int(self.param("hidden_size"))
+        self.nq, self.nkv = int(self.param("num_heads")), int(self.param("num_kv_heads"))
+        self.d = int(self.param("head_dim"))
+        self.dv = int(g("value_dim") or self.d)
+        self.scale = float(self.param("scale"))
+        self.chunk = int(g("chunk")) if g("chunk") else None
+        self.qk_norm = bool(g("qk_norm", False))
+        self.eps = float(g("eps", 0.0))
+        self.value_blend = bool(g("value_blend", False))
+        self.head_gate = bool(g("head_gate", False))
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} query heads cannot share {self.nkv} key/value heads")
+        if not (0 < self.d <= 1024 and 0 < self.dv <= 512):
+            raise ValueError(f"head sizes {self.d} (keys, up to 1024) and {self.dv} (values, up to 512)")
+        self.q_off, self.k_off = 0, self.nq * self.d
+        self.v_off = self.k_off + self.nkv * self.d
+        self.g_off = self.v_off + self.nkv * self.dv
+        self.in_width = self.g_off + (self.nq if self.head_gate else 0)
+        self.out_width = self.nq * self.dv
+
+    def param_decls(self):
+        H, nq, nkv, d, dv = self.hidden, self.nq, self.nkv, self.d, self.dv
+        decls = {"q": ParamDecl((nq * d, H)), "k": ParamDecl((nkv * d, H)), "v": ParamDecl((nkv * dv, H)),
+                 "o": ParamDecl((H, nq * dv))}
+        if self.qk_norm:
+            decls["q.norm"], decls["k.norm"] = ParamDecl((d,), "gain"), ParamDecl((d,), "gain")
+        if self.value_blend:
+            decls["vmix"] = ParamDecl((), "table")
+        if self.head_gate:
+            decls["g"] = ParamDecl((nq, H))
+        return decls
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.d, None, None if self.dv == self.d else self.dv, self.chunk)
+
+    def plan_needs(self):
+        tiles = {ops.ATTENTION_TILE_TOKENS} | ops.rows_attention_tile_sizes(self.nq, self.nkv, self.d, self.dv, False)
+        return PlanNeeds(frozenset(tiles))
+
+    def bind(self, tensors, dtype, device):
+        names = ["q", "k", "v"] + (["g"] if self.head_gate else [])
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in names], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.q_gain = _f32(tensors["q.norm"]) if self.qk_norm else None
+        self.k_gain = _f32(tensors["k.norm"]) if self.qk_norm else None
+        self.blend = _f32(tensors["vmix"]).reshape(1) if self.value_blend else None
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        if out_scale != 1.0:
+            raise ValueError("this attention cannot scale its output")
+        nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
+        rot, freq = _half_rotation(position, d)
+        v_other = None
+        if self.value_blend:
+            # the first blending layer to run in a step leaves its values for the others
+            values = proj[:, self.v_off:self.v_off + nkv * dv]
+            first = ctx.scratch.get("value_blend_source")
+            if first is None:
+                ctx.scratch["value_blend_source"] = values
+            elif first.shape != values.shape:
+                raise ValueError(f"blended values of {tuple(values.shape)} and a first layer's of {tuple(first.shape)}")
+            else:
+                v_other = first
+        group = ctx.groups[cache.group]
+        ops.qk_norm_rope_store(proj, self.q_off, self.k_off, self.v_off, nq, nkv, d, dv, q_gain=self.q_gain,
+                               k_gain=self.k_gain, eps=self.eps, rot=rot, positions=ctx.positions, freq=freq,
+                               v_other=v_other, blend=self.blend if v_other is not None else None,
+                               slots=group.slots if cache.writes else None,
+                               kcache=cache.k if cache.writes else None, vcache=cache.v if cache.writes else None)
+        q = proj[:, self.q_off:self.q_off + nq * d]
+        if not self.head_gate:
+            ops.attention_ext(q, out, cache, ctx, nq, nkv, d, dv, self.scale, chunk=self.chunk or 0)
+            return
+        heads = torch.empty((ctx.n_tokens, nq * dv), dtype=proj.dtype, device=proj.device)
+        ops.attention_ext(q, heads, cache, ctx, nq, nkv, d, dv, self.scale, chunk=self.chunk or 0)
+        ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq], out, "sigmoid", 1.0, per=dv)
+
 # ----------------------------------------------------------------------------- gated linear attention
 
 
@@ -217,6 +333,163 @@ class GatedLinearAttention(ProjectedMixer):
         ops.headnorm_gate(o, self.norm_gain, proj[:, self.g_off:self.g_off + hv], out, self.heads, self.dv,
                           self.eps, "silu", out_scale)
 
+
+
+# ----------------------------------------------------------------------------- retention
+
+
+class Retention(ProjectedMixer):
+    """Linear attention with one fixed decay per head and neither softmax nor denominator: per head a
+    matrix state ``S [key_dim, value_dim]`` in fp32, ``S_t = decay_h S_(t-1) + k_t v_t^T``, ``o_t = S_t^T q_t``.
+    Queries and keys are rotated by the position (a ``RotaryPosition``, half layout, or none) and the
+    keys multiplied by ``key_dim^-1/2`` afterwards.  Each head's ``o`` is divided by its root mean square
+    over ``value_dim``; the heads are multiplied by ``silu(W_g h)`` and projected.
+
+    params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``decay`` (one number per head), ``eps``.
+    tensors: ``q``, ``k``, ``v``, ``g``, ``o``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.dk, self.dv = int(self.param("key_dim")), int(self.param("value_dim"))
+        self.decay = [float(a) for a in self.param("decay")]
+        self.eps = float(self.param("eps"))
+        if len(self.decay) != self.heads:
+            raise ValueError(f"{len(self.decay)} decays for {self.heads} heads")
+        if not 0 < self.dk <= 256:
+            raise ValueError(f"key size {self.dk} must lie in [1, 256]")
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        self.q_off, self.k_off, self.v_off, self.g_off = 0, hk, 2 * hk, 2 * hk + hv
+        self.in_width = 2 * hk + 2 * hv
+        self.out_width = hv
+
+    def param_decls(self):
+        H, hk, hv = self.hidden, self.heads * self.dk, self.heads * self.dv
+        return {"q": ParamDecl((hk, H)), "k": ParamDecl((hk, H)), "v": ParamDecl((hv, H)), "g": ParamDecl((hv, H)),
+                "o": ParamDecl((H, hv))}
+
+    def state_need(self):
+        return StateNeed((self.heads, self.dk, self.dv), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.head_decay = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(device)
+        self.unit_gain = torch.ones(self.dv, dtype=torch.float32, device=device)
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        rot, freq = _half_rotation(position, self.dk)
+        if rot:
+            ops.qk_norm_rope_store(proj, self.q_off, self.k_off, None, self.heads, self.heads, self.dk, self.dv,
+                                   rot=rot, positions=ctx.positions, freq=freq)
+        # the keys' factor rides on the queries: o is linear in both
+        o = ops.gla_scan(proj[:, self.q_off:self.q_off + hk], proj[:, self.k_off:self.k_off + hk],
+                         proj[:, self.v_off:self.v_off + hv], None, None, 1.0, self.dk ** -0.5, self.heads, self.dk,
+                         self.dv, cache.state, ctx, head_decay=self.head_decay)
+        ops.headnorm_gate(o, self.unit_gain, proj[:, self.g_off:self.g_off + hv], out, self.heads, self.dv, self.eps,
+                          "silu", out_scale)
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+
+
+class ChannelDeltaRule(ProjectedMixer):
+    """The gated delta rule with a decay per head and key channel.  ``q = W_q h`` and ``k = W_k h``
+    (``num_kv_heads`` heads of ``key_dim``; head ``h`` uses q/k head ``h // (num_heads / num_kv_heads)``)
+    and ``v = W_v h`` (``num_heads`` heads of ``value_dim``) each pass a causal convolution per channel over
+    ``conv_taps`` tokens (the last tap meets the current token; zeros before the start) and SiLU; q and k
+    become unit vectors per head (``x / sqrt(sum x^2 + unit_eps)``), q also times ``key_dim^-1/2``.  With
+    ``beta = sigmoid(W_b h)`` per head and ``g = exp(-exp(A_log) * softplus(W_a2 (W_a1 h) + dt_bias))`` per
+    head and key channel, per head on its fp32 state ``S [key_dim, value_dim]``:
+    ``S <- diag(g) S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``.  Each head's ``o`` gets an RMS
+    norm over ``value_dim`` with one gain shared by the heads, times ``sigmoid(W_g2 (W_g1 h))``; then ``W_o``.
+    The state (fp32, per request) is the convolution's last ``conv_taps - 1`` inputs, then ``S``.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``key_dim``, ``value_dim``, ``conv_taps``, ``eps``;
+    optional ``unit_eps`` (default 1e-6), ``decay_rank`` and ``gate_rank`` (None: what the checkpoint has).
+    tensors: ``q``, ``q.conv``, ``k``, ``k.conv``, ``v``, ``v.conv``, ``b``, ``A_log``, ``norm``, ``a1``, ``a2``,
+    ``dt_bias``, ``g1``, ``g2``, ``o``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = self.spec.params.get
+        self.hidden = int(self.param("hidden_size"))
+        self.heads, self.kv_heads = int(self.param("num_heads")), int(self.param("num_kv_heads"))
+        self.dk, self.dv = int(self.param("key_dim")), int(self.param("value_dim"))
+        self.taps = int(self.param("conv_taps"))
+        self.eps = float(self.param("eps"))
+        self.unit_eps = float(g("unit_eps", 1e-6))
+        self.rank_a = int(g("decay_rank")) if g("decay_rank") else None
+        self.rank_g = int(g("gate_rank")) if g("gate_rank") else None
+        if self.heads % self.kv_heads:
+            raise ValueError(f"{self.heads} heads cannot share {self.kv_heads} query/key heads")
+        if not 0 < self.dk <= 256:
+            raise ValueError(f"key size {self.dk} must lie in [1, 256]")
+        if not 1 <= self.taps <= 16:
+            raise ValueError(f"{self.taps} convolution taps (1 to 16 are taken)")
+        gk, hv = self.kv_heads * self.dk, self.heads * self.dv
+        self.q_off, self.k_off, self.v_off = 0, gk, 2 * gk
+        self.conv_width = 2 * gk + hv                  # the channels that pass the convolution: q, k, v
+        self.b_off = self.conv_width
+        self.a_off = self.b_off + self.heads
+        self.out_width = hv
+        self.state_offset = (self.taps - 1) * self.conv_width
+
+    @property
+    def in_width(self) -> int:
+        return self.a_off + self.rank_a + self.rank_g
+
+    def param_decls(self):
+        H, gk, hv, hk = self.hidden, self.kv_heads * self.dk, self.heads * self.dv, self.heads * self.dk
+        return {"q": ParamDecl((gk, H)), "q.conv": ParamDecl((gk, self.taps), "table"),
+                "k": ParamDecl((gk, H)), "k.conv": ParamDecl((gk, self.taps), "table"),
+                "v": ParamDecl((hv, H)), "v.conv": ParamDecl((hv, self.taps), "table"),
+                "b": ParamDecl((self.heads, H)), "A_log": ParamDecl((self.heads,), "table"),
+                "norm": ParamDecl((self.dv,), "gain"),
+                "a1": ParamDecl((self.rank_a, H)), "a2": ParamDecl((hk, self.rank_a)),
+                "dt_bias": ParamDecl((hk,), "table"),
+                "g1": ParamDecl((self.rank_g, H)), "g2": ParamDecl((hv, self.rank_g)),
+                "o": ParamDecl((H, hv))}
+
+    def state_need(self):
+        return StateNeed((self.state_offset + self.heads * self.dk * self.dv,), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        self.rank_a, self.rank_g = int(tensors["a1"].shape[0]), int(tensors["g1"].shape[0])
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in ("q", "k", "v", "b", "a1", "g1")],
+                              dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.conv_w = torch.cat([_f32(tensors[n]) for n in ("q.conv", "k.conv", "v.conv")], dim=0).contiguous()
+        self.a2 = Linear(_as_compute(tensors["a2"], dtype).contiguous())
+        self.g2 = Linear(_as_compute(tensors["g2"], dtype).contiguous())
+        self.dt_bias, self.a_log = _f32(tensors["dt_bias"]), _f32(tensors["A_log"])
+        self.norm_gain = _f32(tensors["norm"])
+        self.finish_bind()
+
+    @staticmethod
+    def _aligned(t: torch.Tensor) -> torch.Tensor:
+        return t if (t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0) else t.contiguous()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position):
+        if position is not None:
+            raise ValueError("this mixer takes no position part: the order of the tokens is in its state")
+        gk, hv, C = self.kv_heads * self.dk, self.heads * self.dv, self.conv_width
+        x = proj[:, :C]
+        u = torch.empty((ctx.n_tokens, C), dtype=proj.dtype, device=proj.device)
+        ops.causal_conv(x, None, self.conv_w, None, cache.state, ctx, u, act="silu")
+        z = self.a2(self._aligned(proj[:, self.a_off:self.a_off + self.rank_a]), out_dtype=torch.float32)
+        gate = self.g2(self._aligned(proj[:, self.a_off + self.rank_a:self.a_off + self.rank_a + self.rank_g]))
+        o = ops.delta_scan(u[:, self.q_off:self.q_off + gk], u[:, self.k_off:self.k_off + gk],
+                           u[:, self.v_off:self.v_off + hv], z, self.dt_bias, self.a_log,
+                           proj[:, self.b_off:self.b_off + self.heads], self.dk ** -0.5, self.unit_eps, self.heads,
+                           self.kv_heads, self.dk, self.dv, cache.state, self.state_offset, ctx, conv_in=x,
+                           taps=self.taps)
+        ops.headnorm_gate(o, self.norm_gain, gate, out, self.heads, self.dv, self.eps, "sigmoid", out_scale)
 
 # ----------------------------------------------------------------------------- real-gated linear recurrent unit
 
@@ -344,4 +617,7 @@ class SideBySide(Mixer):
 register_mixer("gated_window_attention", GatedWindowAttention, replace=True)
 register_mixer("gated_linear_attention", GatedLinearAttention, replace=True)
 register_mixer("rglru", RealGatedLinearRecurrence, replace=True)
+register_mixer("chunk_attention", ChunkAttention, replace=True)
+register_mixer("retention", Retention, replace=True)
+register_mixer("channel_delta_rule", ChannelDeltaRule, replace=True)
 register_mixer("side_by_side", SideBySide, replace=True)

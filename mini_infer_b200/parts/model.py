@@ -98,9 +98,10 @@ class DecoderModel:
     def ignorable_tensors(self) -> set[str]:
         """Names a checkpoint may carry although nothing reads them (a tied head's copy)."""
         head = self.head
+        names = set(self.spec.ignorable)
         if getattr(head, "tied", False):
-            return {head.spec.tensor_name("weight")}
-        return set()
+            names.add(head.spec.tensor_name("weight"))
+        return names
 
     def cache_needs(self) -> list[CacheLayerNeed]:
         needs: dict[int, CacheLayerNeed] = {}

@@ -76,6 +76,7 @@ class ModelSpec:
     head: PartSpec
     schedule: tuple[ScheduleEntry, ...] = ()
     max_positions: int | None = None
+    ignorable: tuple[str, ...] = ()     # tensor names a checkpoint may carry although nothing reads them
 
     def __post_init__(self) -> None:
         if not self.schedule:
