@@ -15,12 +15,20 @@
 //            and up to 128 rows (token, head-in-group) that share a key/value head; each
 //            warp owns 16 rows and walks all keys up to the causal limit.
 //
-// A query at absolute position p sees keys j with max(0, p - window + 1) <= j <= p.
+// A query at absolute position p sees keys j with first_visible(p, window) <= j <= p: with window > 0 the
+// last `window` positions, with window < 0 its own chunk of -window positions (chunks counted from
+// position 0), with window = 0 all of them.
 // Layouts are those of attention_generic.cu (cache pages are [nkv, page_size, d], so the keys of a
 // page lie together per key/value head and a 64-key chunk is read as a few long runs).
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
+
+__device__ __forceinline__ int first_visible(int p, int window) {
+  if (window > 0) return max(0, p - window + 1);
+  if (window < 0) return p > 0 ? (p / -window) * -window : 0;
+  return 0;
+}
 
 #define KCHUNK 64
 #define NTHREADS 128
@@ -372,7 +380,7 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restri
   const int b = blockIdx.z;
   const int kl = kv_len[b];
   const int tok = q_start[b];
-  const int lo = window > 0 ? max(0, kl - window) : 0;  // the query sits at position kl - 1
+  const int lo = first_visible(kl - 1, window);  // the query sits at position kl - 1
   const int c_first = lo / KCHUNK, c_end = (kl + KCHUNK - 1) / KCHUNK;
   // A slice is the same number of chunks for every request when the caller planned one (a
   // short request then fills fewer slices and a long one is cut into all of them); never
@@ -778,7 +786,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
   // chunks per request, and their running sum (one warp; B is at most a few hundred)
   for (int b = tid; b < B; b += (ROPE ? BAL_THREADS : DEC_THREADS)) {
     const int kl = kv_len[b];
-    const int lo = window > 0 ? max(0, kl - window) : 0;   // (a window skips the chunks below it)
+    const int lo = first_visible(kl - 1, window);   // (a window skips the chunks below it)
     cum[b + 1] = (kl + KCHUNK - 1) / KCHUNK - lo / KCHUNK;
   }
   __syncthreads();
@@ -843,7 +851,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
       const int len = balanced_part(i, i1, cum, B, U, ov, b, u, c_rel, seg, n_b);
       const int kvh = u / hblocks;
       const int kl = kv_len[b];
-      const int lo = window > 0 ? max(0, kl - window) : 0;
+      const int lo = first_visible(kl - 1, window);
       const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
       for (int s = 0; s < seg && ok; ++s, ++it) {
         const int c = lo / KCHUNK + c_rel + s, st = it % DEC_STAGES;
@@ -945,7 +953,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     const int heads_here = min(DEC_HEADS, g - hb * DEC_HEADS);
     const int head0 = kvh * g + hb * DEC_HEADS;
     const int kl = kv_len[b], tok = q_start[b];
-    const int lo = window > 0 ? max(0, kl - window) : 0;
+    const int lo = first_visible(kl - 1, window);
 
     // Q as the B operand: lane (qd, t4) holds head qd, dims ks*16 + 2*t4 + {0,1} and + 8
     uint32_t qb[DMAX / 16][2];
@@ -1210,7 +1218,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int ntok = min(tt, ql - tok0);
   const int p_first = kl - ql + tok0;
   const int hi = p_first + ntok;  // one past the last key any row of the tile sees
-  const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  const int lo = first_visible(p_first, window);
   const int heads_here = min(gb, g - hb * gb);
   const int* table = block_table + (size_t)(table_rows ? table_rows[b] : b) * bt_stride;
 
@@ -1239,13 +1247,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
       const int tk = R / gb, mem = R - tk * gb;
       rvalid[mt][hr] = tk < ntok && mem < heads_here;
       prow[mt][hr] = p_first + tk;
-      lorow[mt][hr] = window > 0 ? max(0, prow[mt][hr] - window + 1) : 0;
+      lorow[mt][hr] = first_visible(prow[mt][hr], window);
     }
   // the warp's rows span tokens [wt0, wt1]
   const int wt0 = row0 / gb, wt1 = min(ntok - 1, (row0 + 16 * MT - 1) / gb);
   const bool warp_active = wt0 < ntok;
   const int warp_hi = p_first + wt1 + 1;                                   // one past its last visible key
-  const int warp_lo = window > 0 ? max(0, p_first + wt0 - window + 1) : 0;  // its first visible key
+  const int warp_lo = first_visible(p_first + wt0, window);  // its first visible key
 
   float m_run[MT][2], l_run[MT][2];
   float o[MT][DMAX / 8][4];
@@ -1338,7 +1346,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
       // few on the diagonal and at a window's edge) needs no mask.  Scores stay unscaled; the
       // scale is folded into the exponent's multiply-add: p = 2^(s * sc - m), m = sc * max(s).
       const bool interior = key0 + KCHUNK - 1 <= p_first + wt0 &&
-                            key0 >= (window > 0 ? max(0, p_first + wt1 - window + 1) : 0);
+                            key0 >= first_visible(p_first + wt1, window);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         if (!interior) {
@@ -1459,7 +1467,8 @@ static int check_common(const void* q, int q_stride, const void* out, int out_st
   }
   if (d <= 0 || d % 16 != 0 || d > 256) MI_REFUSE("attention: head size %d is not a multiple of 16 in [16, 256]", d);
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0) MI_REFUSE("attention: %d query heads cannot share %d key/value heads", nq, nkv);
-  if (page_size <= 0 || window < 0) MI_REFUSE("attention: bad page size %d or window %d", page_size, window);
+  if (page_size <= 0) MI_REFUSE("attention: bad page size %d", page_size);
+  (void)window;   // any value is a mask: a window (> 0), chunks (< 0) or none
   if (!mi_aligned(q, 16) || q_stride % 8 != 0) MI_REFUSE("attention: queries must be 16-byte aligned with a row stride that is a multiple of 8");
   if (!mi_aligned(out, 4) || out_stride % 2 != 0) MI_REFUSE("attention: output rows must be 4-byte aligned");
   if (!mi_aligned(kcache, 16) || !mi_aligned(vcache, 16)) MI_REFUSE("attention: cache must be 16-byte aligned");

@@ -261,7 +261,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ q_start, const int* __restrict__ q_len,
                             const int* __restrict__ kv_len, const int* __restrict__ tile_req,
                             const int* __restrict__ tile_tok0, int nq, int nkv, int d, float scale, int window,
-                            int gb, int tt, const float* __restrict__ sinks, const float* __restrict__ slopes) {
+                            int chunk, int gb, int tt, const float* __restrict__ sinks, const float* __restrict__ slopes) {
   mi_pdl_enter();   // inputs come from the kernels before this one
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -289,7 +289,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int ntok = min(tt, ql - tok0);
   const int p_first = kl - ql + tok0;
   const int hi = p_first + ntok;                   // one past the last key any row of the block sees
-  const int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  // the lowest key any row sees: the first row's bound (a window's and a chunk's start both grow with the row)
+  int lo = window > 0 ? max(0, p_first - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (p_first / chunk) * chunk);
   const int heads_here = min(gb, g - hb * gb);
   const int c0 = lo / KC, c1 = (hi + KC - 1) / KC;
   const int n_chunks = c1 - c0;
@@ -446,7 +448,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int tk = R / gb, mem = R - tk * gb;
     const bool rvalid = tk < ntok && mem < heads_here;
     const int prow = p_first + tk;
-    const int lorow = window > 0 ? max(0, prow - window + 1) : 0;
+    int lorow = window > 0 ? max(0, prow - window + 1) : 0;
+    if (chunk > 0) lorow = max(lorow, (prow / chunk) * chunk);   // only the keys of the row's own chunk of positions
     // the tile's own range of tokens: chunks past its last row's position are skipped wholesale
     const int t_first = p_first + (t * ROWS) / gb, t_last = min(hi - 1, p_first + (t * ROWS + ROWS - 1) / gb);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -482,7 +485,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
         for (int j = 0; j < 64; ++j) s[j] = fmaf(bias_per_step, (float)j - back, s[j]);
       }
-      const bool interior = key0 + KC - 1 <= t_first && key0 >= (window > 0 ? max(0, t_last - window + 1) : 0) && key0 >= lo;
+      const bool interior = key0 + KC - 1 <= t_first && key0 >= (window > 0 ? max(0, t_last - window + 1) : 0) &&
+                            key0 >= (chunk > 0 ? (t_last / chunk) * chunk : 0) && key0 >= lo;
       if (!interior || !rvalid) {
 #pragma unroll
         for (int j = 0; j < 64; ++j)
@@ -690,13 +694,16 @@ extern "C" int mi_attention_prefill_tc_tile_tokens(int g) {
 // `sinks` / `slopes` (fp32 [nq], either may be null): a score per head that joins the softmax's
 // denominator without a key or a value, and a distance bias (the scaled score of a key `dist`
 // positions back is lowered by slopes[h] * dist).
-extern "C" int mi_attention_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
-                                           const void* vcache, long long n_pages, const int* block_table, int bt_stride,
-                                           const int* table_rows, int page_size, const int* q_start, const int* q_len,
-                                           const int* kv_len, const int* tile_req, const int* tile_tok0, int n_tiles,
-                                           int tile_tokens, int nq, int nkv, int d, float scale, int window,
-                                           const float* sinks, const float* slopes, cudaStream_t stream) {
+// `chunk` > 0: a query at position p sees only the keys of its own chunk of positions, j >= (p / chunk) * chunk.
+extern "C" int mi_attention_prefill_tc_masked(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                              const void* vcache, long long n_pages, const int* block_table,
+                                              int bt_stride, const int* table_rows, int page_size, const int* q_start,
+                                              const int* q_len, const int* kv_len, const int* tile_req,
+                                              const int* tile_tok0, int n_tiles, int tile_tokens, int nq, int nkv, int d,
+                                              float scale, int window, int chunk, const float* sinks,
+                                              const float* slopes, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (chunk < 0) MI_REFUSE("attention_tc: bad chunk size %d", chunk);
   if (!mi_attention_prefill_tc_supported(nq, nkv, d, page_size))
     MI_REFUSE("attention_tc: sizes not taken (heads %d/%d, head size %d, pages of %d)", nq, nkv, d, page_size);
   if (!(scale > 0.f)) MI_REFUSE("attention_tc: the score scale must be positive");
@@ -725,8 +732,19 @@ extern "C" int mi_attention_prefill_tc_ext(const void* q, int q_stride, void* ou
   dim3 grid((unsigned)n_blocks);
   MI_LAUNCH((kern), grid, TC_THREADS, smem, stream, map_k, map_v, (const bf16*)q, q_stride, (bf16*)out, out_stride,
             block_table, bt_stride, table_rows, page_size, page_shift, q_start, q_len, kv_len, tile_req, tile_tok0, nq, nkv, d, scale,
-            window, gb, NTILE * ROWS / gb, sinks, slopes);
+            window, chunk, gb, NTILE * ROWS / gb, sinks, slopes);
   MI_RETURN_LAUNCH_STATUS();
+}
+
+extern "C" int mi_attention_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* kcache,
+                                           const void* vcache, long long n_pages, const int* block_table, int bt_stride,
+                                           const int* table_rows, int page_size, const int* q_start, const int* q_len,
+                                           const int* kv_len, const int* tile_req, const int* tile_tok0, int n_tiles,
+                                           int tile_tokens, int nq, int nkv, int d, float scale, int window,
+                                           const float* sinks, const float* slopes, cudaStream_t stream) {
+  return mi_attention_prefill_tc_masked(q, q_stride, out, out_stride, kcache, vcache, n_pages, block_table, bt_stride,
+                                        table_rows, page_size, q_start, q_len, kv_len, tile_req, tile_tok0, n_tiles,
+                                        tile_tokens, nq, nkv, d, scale, window, 0, sinks, slopes, stream);
 }
 
 extern "C" int mi_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* kcache,

@@ -211,6 +211,10 @@ def _sig_attention_tc(lib: ctypes.CDLL) -> None:
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
         c_void_p, c_void_p, c_void_p]
+    lib.mi_attention_prefill_tc_masked.argtypes = [
+        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+        c_void_p, c_void_p, c_void_p]
     lib.mi_attention_prefill_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
     lib.mi_attention_tc_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
@@ -613,7 +617,8 @@ def decode_rope_fusable(q_dtype: torch.dtype, head_dim: int, decode_only: bool, 
 
 
 def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq: int, nkv: int,
-              head_dim: int, scale: float, window: int = 0, rope_table: torch.Tensor | None = None) -> None:
+              head_dim: int, scale: float, window: int = 0, rope_table: torch.Tensor | None = None,
+              chunk: int = 0) -> None:
     """Attention of this step's queries over one cache layer.
 
     ``cache`` is a ``LayerCache`` (its ``k``/``v`` pages and group index), ``ctx`` the
@@ -621,13 +626,20 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
     bfloat16 runs the tensor-core kernels: the balanced decode kernel when every request brings
     one token, otherwise the tcgen05 prefill kernel where it takes the sizes and the mma.sync
     prefill kernel elsewhere.  ``rope_table`` (only where ``decode_rope_fusable``): q, k, v are
-    un-rotated and not yet stored; the decode kernel does both.
+    un-rotated and not yet stored; the decode kernel does both.  ``window`` > 0: a query sees the last
+    ``window`` positions only; ``chunk`` > 0: only the keys of its own chunk of positions,
+    ``j >= (p // chunk) * chunk`` (one of the two; the mma.sync kernels take a chunk as a negative window).
     """
     group = ctx.groups[cache.group]
+    if window and chunk:
+        raise KernelError("attention: a window or chunks, not both")
+    if chunk < 0 or window < 0:
+        raise KernelError("attention: a window and a chunk size are positive")
     if q.dtype == torch.bfloat16:
+        mask = -int(chunk) if chunk else int(window)
         if ctx.decode_only:
             attention_decode_balanced(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
-                                      ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, window,
+                                      ctx.q_start, ctx.kv_len, ctx.n_requests, nq, nkv, head_dim, scale, mask,
                                       table_rows=group.table_rows, rope_table=rope_table,
                                       store_kv=bool(cache.writes))
         else:
@@ -641,13 +653,19 @@ def attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache, ctx, nq:
                 # all blocks), the prompt portions through the prefill kernel; disjoint rows of `out`
                 attention_decode_balanced(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                                           ctx.single_q_start, ctx.single_kv_len, ctx.n_single, nq, nkv, head_dim,
-                                          scale, window, table_rows=ctx.single_rows)
+                                          scale, mask, table_rows=ctx.single_rows)
                 tile_req, tile_tok0, n_tiles = ctx.tiles_multi[tt]
-            (attention_prefill_tc if tc else attention_prefill)(
-                q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
-                ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
-                nq, nkv, head_dim, scale, window, table_rows=group.table_rows)
+            if tc:
+                attention_prefill_tc(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                                     ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
+                                     nq, nkv, head_dim, scale, window, table_rows=group.table_rows, chunk=chunk)
+            else:
+                attention_prefill(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
+                                  ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles, tt,
+                                  nq, nkv, head_dim, scale, mask, table_rows=group.table_rows)
         return
+    if chunk:
+        raise KernelError("attention: float32 chunks go through attention_ext")
     tile_req, tile_tok0, n_tiles = ctx.q_tiles(ATTENTION_TILE_TOKENS)
     attention_generic(q, q_stride, out, cache.k, cache.v, group.block_table, group.page_size,
                       ctx.q_start, ctx.q_len, ctx.kv_len, tile_req, tile_tok0, n_tiles,
@@ -814,11 +832,12 @@ def prefill_tc_supported(nq: int, nkv: int, head_dim: int, page_size: int) -> bo
 def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, q_len, kv_len,
                          tile_req, tile_tok0, n_tiles, tile_tokens, nq, nkv, head_dim, scale, window=0,
                          table_rows=None, sinks: torch.Tensor | None = None,
-                         slopes: torch.Tensor | None = None) -> None:
+                         slopes: torch.Tensor | None = None, chunk: int = 0) -> None:
     """bfloat16 attention of query portions over the paged cache on tcgen05 (attention_tc.cu);
     same arguments as ``attention_prefill``, and optionally ``sinks`` / ``slopes`` (fp32 ``[nq]``: a
     score per head in the softmax's denominator without a key; a distance bias ``slope * (i - j)``
-    taken off the scaled scores)."""
+    taken off the scaled scores) and ``chunk`` (> 0: a query at position ``p`` sees only the keys of its
+    own chunk of positions, ``j >= (p // chunk) * chunk``)."""
     _cuda(q, out, kcache, vcache, block_table, q_start, q_len, kv_len, tile_req, tile_tok0, table_rows, sinks, slopes)
     for name, t in (("sinks", sinks), ("slopes", slopes)):
         if t is not None and (t.dtype != torch.float32 or t.numel() != nq or not t.is_contiguous()):
@@ -830,11 +849,11 @@ def attention_prefill_tc(q, q_stride, out, kcache, vcache, block_table, page_siz
                            ("kv_len", kv_len), ("tile_req", tile_req), ("tile_tok0", tile_tok0),
                            ("table_rows", table_rows)))
     lib = _waiting_lib("attention_tc", q.device)
-    rc = lib.mi_attention_prefill_tc_ext(
+    rc = lib.mi_attention_prefill_tc_masked(
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), int(kcache.shape[0]),
         _ptr(block_table), block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(q_len), _ptr(kv_len),
         _ptr(tile_req), _ptr(tile_tok0), int(n_tiles), int(tile_tokens), nq, nkv, head_dim, float(scale),
-        int(window), _ptr(sinks), _ptr(slopes), _stream())
+        int(window), int(chunk), _ptr(sinks), _ptr(slopes), _stream())
     _finish(lib, rc, "attention_prefill_tc")
 
 

@@ -228,7 +228,25 @@ class ChunkAttention(ProjectedMixer):
 
     def plan_needs(self):
         tiles = {ops.ATTENTION_TILE_TOKENS} | ops.rows_attention_tile_sizes(self.nq, self.nkv, self.d, self.dv, False)
+        if self._tensor_core_sizes():
+            tiles |= set(ops.attention_tile_sizes(self.nq // self.nkv))
         return PlanNeeds(frozenset(tiles))
+
+    def _tensor_core_sizes(self) -> bool:
+        """Sizes the tensor-core attention kernels take: keys and values of one size, a multiple of 16."""
+        return self.d == self.dv and self.d % 16 == 0 and 16 <= self.d <= 256
+
+    def _attend(self, q, heads, cache, ctx):
+        """bfloat16 with sizes the tensor-core kernels take and aligned rows: those kernels (the balanced
+        decode kernel, tcgen05 or mma.sync for prompt portions; scores and softmax in fp32, as everywhere);
+        else the kernel for keys and values of two sizes or the CUDA-core kernel."""
+        if (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0 and heads.is_contiguous()
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+            ops.attention(q, q.stride(0), heads, cache, ctx, self.nq, self.nkv, self.d, self.scale,
+                          chunk=self.chunk or 0)
+        else:
+            ops.attention_ext(q, heads, cache, ctx, self.nq, self.nkv, self.d, self.dv, self.scale,
+                              chunk=self.chunk or 0)
 
     def bind(self, tensors, dtype, device):
         names = ["q", "k", "v"] + (["g"] if self.head_gate else [])
@@ -263,10 +281,10 @@ class ChunkAttention(ProjectedMixer):
                                kcache=cache.k if cache.writes else None, vcache=cache.v if cache.writes else None)
         q = proj[:, self.q_off:self.q_off + nq * d]
         if not self.head_gate:
-            ops.attention_ext(q, out, cache, ctx, nq, nkv, d, dv, self.scale, chunk=self.chunk or 0)
+            self._attend(q, out, cache, ctx)
             return
         heads = torch.empty((ctx.n_tokens, nq * dv), dtype=proj.dtype, device=proj.device)
-        ops.attention_ext(q, heads, cache, ctx, nq, nkv, d, dv, self.scale, chunk=self.chunk or 0)
+        self._attend(q, heads, cache, ctx)
         ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq], out, "sigmoid", 1.0, per=dv)
 
 # ----------------------------------------------------------------------------- gated linear attention

@@ -168,15 +168,20 @@ def route(z: torch.Tensor, router: dict):
     """From one token's router logits: the chosen experts and their weights.  Scores are the
     softmax over all experts; experts lie in ``groups.count`` equal groups of neighbours, a group
     counts as its best score, only the best ``groups.keep`` groups may give experts; the ``top``
-    best of those are chosen and weighted by their scores over the sum of these, times ``scale``."""
+    best of those are chosen and weighted by their scores over the sum of these, times ``scale``.
+    Also returns the scores with the experts of other groups struck out, and the kept groups' margin."""
     E, top = router["experts"], router["top"]
     s = torch.softmax(z, dim=0)
     allowed = torch.ones(E, dtype=torch.bool)
     groups = router.get("groups")
+    group_margin = float("inf")
     if groups:
         n, keep = groups["count"], groups["keep"]
         best = s.reshape(n, E // n).max(dim=1).values
         kept = torch.topk(best, keep).indices
+        if keep < n:
+            ordered = torch.sort(best, descending=True).values
+            group_margin = float(torch.log(ordered[keep - 1] / ordered[keep]))
         allowed = torch.zeros(n, E // n, dtype=torch.bool)
         allowed[kept] = True
         allowed = allowed.reshape(E)
@@ -184,20 +189,27 @@ def route(z: torch.Tensor, router: dict):
     idx = torch.topk(masked, top).indices
     w = s[idx]
     w = w / (w.sum() + 1e-20) * router.get("scale", 1.0)
-    return idx.tolist(), w, masked
+    return idx.tolist(), w, masked, group_margin
 
 
 def moe(h: torch.Tensor, W: dict, mlp: dict, margins: list | None = None) -> torch.Tensor:
     """Every token through its chosen experts ``W_down (silu(W_gate h) * W_up h)``, weighted.
-    ``margins`` collects how far the last chosen score lies above the best one left out."""
+    ``margins`` collects per token how far the last chosen expert's logit lies above the best one's left out
+    (the logarithm of the ratio of their scores; or the last kept group's above the best one's left out, if
+    that is closer)."""
     router = mlp["router"]
     z = h @ W["router"].T
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        idx, w, masked = route(z[t], router)
-        if margins is not None and router["top"] < router["experts"]:
-            ordered = torch.sort(masked, descending=True).values
-            margins.append(float(ordered[router["top"] - 1] - ordered[router["top"]]))
+        idx, w, masked, group_margin = route(z[t], router)
+        if margins is not None:
+            margin = group_margin
+            if router["top"] < router["experts"]:
+                ordered = torch.sort(masked, descending=True).values
+                last, nxt = ordered[router["top"] - 1], ordered[router["top"]]
+                if nxt > 0:                                  # (an expert struck out is no rival)
+                    margin = min(margin, float(torch.log(last / nxt)))
+            margins.append(margin)
         x = h[t:t + 1]
         for wt, e in zip(w, idx):
             y = (silu(x @ W[f"e{e}.gate"].T) * (x @ W[f"e{e}.up"].T)) @ W[f"e{e}.down"].T

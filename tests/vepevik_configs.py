@@ -67,7 +67,7 @@ CONFIGS = {
                  delta(3, 1, 7, 5, 1, experts(3, 2, 10, 1.0, (3, 3))),
                  attention(2, 1, 20, 28, 5, None, 0.2, False, None),
                  retention(2, 10, 6, (0.999, 0.05), None, experts(2, 1, 32)),
-                 attention(1, 1, 32, 24, None, (16, 7.0), 0.18, True, dense(20, 0.5)),
+                 attention(3, 3, 32, 8, None, (16, 7.0), 0.18, True, dense(20, 0.5)),
                  delta(2, 2, 24, 36, 5, experts(6, 2, 12, 1.25, (2, 1)))],
                 vocab=47, width=36, eps=1e-5),
 }
@@ -126,7 +126,7 @@ def random_state(cfg: dict, seed: int, ranks=(4, 4)) -> dict[str, torch.Tensor]:
                        q + "down": mat(H, mlp["ff"])})
         elif mlp:
             ff = mlp["expert"]["ff"]
-            st[q + "router"] = mat(mlp["router"]["experts"], H, std=2.0 * H ** -0.5)
+            st[q + "router"] = mat(mlp["router"]["experts"], H, std=4.0 * H ** -0.5)
             for e in range(mlp["router"]["experts"]):
                 st.update({f"{q}e{e}.gate": mat(ff, H, std=0.3), f"{q}e{e}.up": mat(ff, H, std=0.3),
                            f"{q}e{e}.down": mat(H, ff)})
