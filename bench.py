@@ -319,6 +319,21 @@ def design_matmul_params(s: dict, layers: int, batch_tokens: int | None) -> floa
     return n_unit * (unit + mlp) + (layers - n_unit) * (left + right + mlp) + s["vocab"] * H
 
 
+def ruvurax_numbers(s: dict, layers: int, batch: int, context: int, tokens: int) -> tuple[float, float]:
+    """(bytes a decode step of the Ruvurax configuration must move, operations of a prefill of ``tokens``)."""
+    n_both = layers // 2
+    window = min(s["window"], tokens)
+    attention = n_both * 4.0 * tokens * window * s["heads"] * s["dim"]   # an upper bound
+    linear = n_both * 4.0 * tokens * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+    flops = 2.0 * tokens * (design_matmul_params(s, layers, None) - s["vocab"] * s["width"]) \
+        + 2.0 * s["vocab"] * s["width"] + attention + linear
+    cache = 2.0 * batch * min(s["window"], context) * 2 * s["kv_heads"] * s["dim"] * n_both
+    state = 8.0 * batch * (n_both * s["r_heads"] * s["r_dim"] * s["r_vdim"]
+                           + (layers - n_both) * s["conv"] * s["unit_width"])
+    nbytes = 2.0 * design_matmul_params(s, layers, batch) + cache + state
+    return nbytes, flops
+
+
 # The Lilulix architecture at the same widths: layers alternate attention in a latent space and
 # distance-bias attention, each beside a dense gated feed-forward; the two middle layers run twice.
 LILULIX_SIZES = {
@@ -363,6 +378,113 @@ def lilulix_numbers(s: dict, runs: list[int], batch: int, context: float, tokens
     attention = sum(tokens * tokens * n * ((d + rd + dv) if i % 2 == 0 else 2 * d) for i in runs)   # causal half of 2 T^2 n (dk + dv)
     flops = 2.0 * tokens * params + 2.0 * s["vocab"] * H + attention
     return nbytes, flops
+
+
+# The Vepevik architecture at the same widths: retention, chunked attention (values blended with the first
+# such layer's), the channel-wise gated delta rule and chunked attention again; the first layer has a dense
+# clamped feed-forward, the others a mixture of experts chosen within the best groups.  Beside it Ruvurax (the
+# closest model: a matrix-state mixer, masked attention and experts) and Llama with the same width, heads, layer
+# count and per-token feed-forward.
+VEPEVIK_SIZES = {
+    "2k": dict(chunk=1024, ranks=16, groups=4, keep=2),
+    "4k": dict(chunk=2048, ranks=32, groups=8, keep=4),
+}
+
+
+def vepevik_design(s: dict, v: dict, layers: int) -> dict:
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5,
+                                     "groups": {"count": v["groups"], "keep": v["keep"]}}, "expert": {"ff": s["ff"]}}
+    dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["shared_ff"], "limit": 7.0}
+    rot = {"base": 10000.0, "dims": s["rot"]}
+    heads, d = s["heads"], s["dim"]
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, heads - 1)) for h in range(heads)]
+    ret = {"type": "retention", "mixer": {"heads": heads, "dim": d, "vdim": d, "decay": decay, "rot": rot}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": s["kv_heads"], "dim": d, "vdim": d,
+                                          "mask": {"size": v["chunk"]}, "rot": rot, "scale": d ** -0.5, "v_mix": True}}
+    delta = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": d, "vdim": d,
+                                                "conv": s["conv"], "ranks": {"decay": v["ranks"], "gate": v["ranks"]}}}
+    order = [ret, att, delta, att]
+    return {"architecture": "Vepevik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "layers": [dict(order[i % 4], mlp=dense if i == 0 else moe) for i in range(layers)]}
+
+
+def vepevik_numbers(s: dict, v: dict, layers: int, batch: int, context: float, tokens: int) -> tuple[float, float]:
+    """(bytes a decode step of ``batch`` requests at ``context`` must move, floating-point operations of a
+    prefill of ``tokens``): weights once (of the experts, those the batch's tokens choose in expectation), the cache
+    rows of a request's own chunk, the matrix states read and written; products, the causal part of the scores
+    inside chunks, and two products per token and state."""
+    H, E, top, ff = s["width"], s["experts"], s["top"], s["ff"]
+    heads, nkv, d, r = s["heads"], s["kv_heads"], s["dim"], v["ranks"]
+    hd = heads * d
+    mix_w = {0: 5 * H * hd, 1: H * (2 * hd + 2 * nkv * d + heads), 3: H * (2 * hd + 2 * nkv * d + heads),
+             2: 4 * H * hd + H * heads + 2 * r * (H + hd)}
+    hit = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))
+    dense_w = 3 * H * (top * ff + s["shared_ff"])
+    params_decode = params_token = 0.0
+    cache = state = attention = recur = 0.0
+    in_chunk = (context % v["chunk"]) or v["chunk"]
+    n_chunks, rest = divmod(tokens, v["chunk"])
+    pairs = n_chunks * v["chunk"] ** 2 / 2.0 + rest ** 2 / 2.0          # (query, key) pairs that see each other
+    for i in range(layers):
+        kind = i % 4
+        params_decode += mix_w[kind] + (dense_w if i == 0 else H * E + hit * 3 * H * ff)
+        params_token += mix_w[kind] + (dense_w if i == 0 else H * E + top * 3 * H * ff)
+        if kind in (1, 3):
+            cache += 2.0 * batch * in_chunk * 2 * nkv * d
+            attention += 4.0 * pairs * heads * d
+        else:
+            state += 8.0 * batch * heads * d * d
+            recur += (4.0 if kind == 0 else 8.0) * tokens * heads * d * d
+    nbytes = 2.0 * (params_decode + s["vocab"] * H) + cache + state
+    flops = 2.0 * tokens * params_token + 2.0 * s["vocab"] * H + attention + recur
+    return nbytes, flops
+
+
+def run_vepevik_designs(args) -> int:
+    import torch
+
+    from mini_infer_b200.engine import ModelRunner
+
+    peaks = load_peaks()
+    warmup = max(3, args.warmup)
+    out = {"scenario": "designs", "design": "vepevik", "dtype": "bf16", "data": "synthetic", "batch": args.batch,
+           "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.design_sizes.split(","):
+        s, v = DESIGN_SIZES[name], VEPEVIK_SIZES[name]
+        layers = args.layers or 4
+        ruvurax, llama = design_configs(s, layers)
+        cap = args.batch * (args.context + args.steps + warmup + 64) + 2 * PREFILL_TOKENS
+        mid = args.context + warmup + args.steps / 2.0
+        row = {"layers": layers}
+        for label, raw in (("vepevik", vepevik_design(s, v, layers)), ("ruvurax", ruvurax), ("llama", llama)):
+            runner = ModelRunner.from_random(raw, seed=0, gain_std=0.0, device="cuda:0", dtype="bfloat16",
+                                             num_blocks=cap // PAGE + 8, block_size=PAGE, max_requests=args.batch,
+                                             cuda_graph=True)
+            ms, launches = time_decode(runner, args.batch, args.context, args.steps, warmup)
+            pms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+            if label == "vepevik":
+                nbytes, flops = vepevik_numbers(s, v, layers, args.batch, mid, PREFILL_TOKENS)
+            elif label == "llama":
+                flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+                nbytes = decode_bytes(raw, layers, args.batch, mid)
+            else:
+                nbytes, flops = ruvurax_numbers(s, layers, args.batch, args.context, PREFILL_TOKENS)
+            row[label] = {
+                "decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4),
+                "decode_gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_frac_of_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pms, 1), "prefill_ms": round(pms, 3),
+                "prefill_frac_of_bf16": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "launches_per_decode_step": launches // max(1, args.steps),
+            }
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
 
 
 def run_lilulix_designs(args) -> int:
@@ -437,16 +559,7 @@ def run_designs(args) -> int:
                 flops = prefill_flops(raw, layers, PREFILL_TOKENS)
                 nbytes = decode_bytes(raw, layers, args.batch, args.context + warmup + args.steps / 2.0)
             else:
-                n_both = layers // 2
-                window = min(s["window"], PREFILL_TOKENS)
-                attention = n_both * 4.0 * PREFILL_TOKENS * window * s["heads"] * s["dim"]   # an upper bound
-                linear = n_both * 4.0 * PREFILL_TOKENS * s["r_heads"] * s["r_dim"] * s["r_vdim"]
-                flops = 2.0 * PREFILL_TOKENS * (design_matmul_params(s, layers, None) - s["vocab"] * s["width"]) \
-                    + 2.0 * s["vocab"] * s["width"] + attention + linear
-                cache = 2.0 * args.batch * min(s["window"], args.context) * 2 * s["kv_heads"] * s["dim"] * n_both
-                state = 8.0 * args.batch * (n_both * s["r_heads"] * s["r_dim"] * s["r_vdim"]
-                                            + (layers - n_both) * s["conv"] * s["unit_width"])
-                nbytes = 2.0 * design_matmul_params(s, layers, args.batch) + cache + state
+                nbytes, flops = ruvurax_numbers(s, layers, args.batch, args.context, PREFILL_TOKENS)
             row[label] = {
                 "decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4),
                 "decode_gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
@@ -893,9 +1006,9 @@ def main() -> int:
                     help="decode: the contract line; long-mixed: many requests of very different lengths "
                          "through the scheduler (a line of its own); serving: the reference's published "
                          "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own); "
-                         "designs: the Ruvurax (or, with --design lilulix, the Lilulix) architecture beside Llama at equal sizes, prefill and decode "
+                         "designs: the Ruvurax (or, with --design, the Lilulix or the Vepevik) architecture beside Llama at equal sizes, prefill and decode "
                          "(a line of its own)")
-    ap.add_argument("--design", default="ruvurax", choices=["ruvurax", "lilulix"],
+    ap.add_argument("--design", default="ruvurax", choices=["ruvurax", "lilulix", "vepevik"],
                     help="designs: which architecture stands beside Llama")
     ap.add_argument("--design-sizes", default="2k,4k", help="designs: which of the sizes " + ",".join(DESIGN_SIZES))
     ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
@@ -925,6 +1038,8 @@ def main() -> int:
         return run_long_mixed(args)
     if args.scenario == "designs":
         args.layers = None if args.layers == default_layers else args.layers
+        if args.design == "vepevik":
+            return run_vepevik_designs(args)
         return run_lilulix_designs(args) if args.design == "lilulix" else run_designs(args)
     warmup = max(3, args.warmup)
 

@@ -33,7 +33,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens held by live requests at any time (each rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: requests live at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 

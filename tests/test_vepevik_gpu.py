@@ -460,12 +460,12 @@ def test_clamped_dense_unit_normalised_embedding_and_gates_per_head(dtype, bound
     assert (out.cpu().double() - ref).abs().max() <= bound / 4 * max(1.0, ref.abs().max())
 
 
-def chunk_runner(chunk, n_tokens, page, dtype="float32"):
-    """A runner of one attention layer (2 query heads on 1 key head, keys of 16, values of 12) whose planner and
-    pages the kernel-level test borrows."""
+def chunk_runner(chunk, n_tokens, page, dtype="float32", sizes=(2, 1, 16, 12)):
+    """A runner of one attention layer (``sizes``: query heads, key heads, key size, value size) whose planner,
+    pages and choice of kernel the kernel-level test borrows."""
     from mini_infer_b200.engine import ModelRunner
 
-    cfg = config([attention(2, 1, 16, 12, chunk, None, 4.0, False, None)], vocab=8, width=16, eps=1e-6)
+    cfg = config([attention(*sizes, chunk, None, 64.0, False, None)], vocab=8, width=16, eps=1e-6)
     runner = ModelRunner.from_state_dict(cfg, random_state(cfg, seed=3), dtype=dtype, block_size=page,
                                          num_blocks=-(-n_tokens // page) + 1, max_requests=2)
     for st in runner.cache.storage:
@@ -473,25 +473,32 @@ def chunk_runner(chunk, n_tokens, page, dtype="float32"):
     return runner
 
 
+# keys and values of two sizes (the kernel for rows of two sizes, or CUDA cores); of one size: in bfloat16 the
+# tensor-core kernels (mma.sync for 32-wide heads, tcgen05 for prompt portions of 64- and 128-wide heads, the balanced
+# kernel for single tokens), with and without shared key heads
+@pytest.mark.parametrize("sizes", [(2, 1, 16, 12), (2, 2, 32, 32), (4, 2, 64, 64), (8, 1, 128, 128)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_chunk_edges_page_borders_and_far_keys(dtype):
+def test_chunk_edges_page_borders_and_far_keys(dtype, sizes):
     """One key is made to stand out (it points where the queries point, all others across): a query in its
     chunk and behind it returns its value, a query of the next chunk or before it does not.  The key sits at a
     chunk's first and last position, at a page's last and first slot, and hundreds of tokens back with no
     chunks at all; the tokens come as one prompt, in portions cut inside chunks, and one by one."""
     from mini_infer_b200.engine import StepEntry
 
-    nq, nkv, d, dv = 2, 1, 16, 12
+    nq, nkv, d, dv = sizes
     td = torch.float32 if dtype == "float32" else torch.bfloat16
 
     def run(chunk, n_tokens, marked, page, portions):
-        runner = chunk_runner(chunk, n_tokens, page, dtype)
+        runner = chunk_runner(chunk, n_tokens, page, dtype, sizes)
+        mixer = runner.model.blocks[0].mixer
+        assert (mixer.chunk, mixer.scale) == (chunk, 64.0)
         runner.add_request("a")
         packed = torch.zeros(n_tokens, (nq + nkv) * d + nkv * dv)
         packed[:, 0:nq * d:d] = 1.0                          # queries: e0
-        packed[:, nq * d + 1] = 1.0                          # keys: e1 ...
-        packed[marked, nq * d + 1] = 0.0
-        packed[marked, nq * d] = 1.0                         # ... the marked key: e0
+        for kh in range(nkv):
+            packed[:, (nq + kh) * d + 1] = 1.0               # keys: e1 ...
+            packed[marked, (nq + kh) * d + 1] = 0.0
+            packed[marked, (nq + kh) * d] = 1.0              # ... the marked key: e0
         packed[:, (nq + nkv) * d:] = 1.0                     # values: ones, the marked value: tens
         packed[marked, (nq + nkv) * d:] = 10.0
         outs, t0 = [], 0
@@ -503,7 +510,7 @@ def test_chunk_edges_page_borders_and_far_keys(dtype):
             ops().qk_norm_rope_store(dev, 0, nq * d, (nq + nkv) * d, nq, nkv, d, dv,
                                      slots=ctx.groups[cache.group].slots, kcache=cache.k, vcache=cache.v)
             out = torch.empty(n, nq * dv, dtype=td, device=DEV)
-            ops().attention_ext(dev[:, :nq * d], out, cache, ctx, nq, nkv, d, dv, 64.0, chunk=chunk or 0)
+            mixer._attend(dev[:, :nq * d], out, cache, ctx)
             outs.append(out.float().cpu())
             t0 += n
         assert t0 == n_tokens
