@@ -34,6 +34,7 @@ def assemble(cfg: VepevikConfig) -> ModelSpec:
     H = cfg.width
     layers = []
     unread = []
+    blending_seen = False
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         m = layer.mixer
@@ -49,10 +50,15 @@ def assemble(cfg: VepevikConfig) -> ModelSpec:
                               "decay_rank": m.decay_rank, "gate_rank": m.gate_rank}, prefix=p + "mix.")
         else:
             assert isinstance(m, ChunkAttentionConfig)
+            blend = m.v_mix
+            if m.v_mix and not blending_seen:
+                # the first blending layer gives its values to the others; its own factor is never used
+                blend, blending_seen = "source", True
+                unread.append(p + "mix.vmix")
             mixer = PartSpec("chunk_attention",
                              {"hidden_size": H, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
                               "value_dim": m.vdim, "scale": m.scale, "chunk": m.chunk, "qk_norm": True, "eps": cfg.eps,
-                              "value_blend": m.v_mix, "head_gate": True}, prefix=p + "mix.")
+                              "value_blend": blend, "head_gate": True}, prefix=p + "mix.")
             position = _rotary(m.rot, m.dim)
         e = layer.mlp
         if e is None:

@@ -178,7 +178,8 @@ class ChunkAttention(ProjectedMixer):
     (``qk_norm``), then the position encoding (a ``RotaryPosition``, half layout, or none); the score is
     ``q . k * scale``.  With ``value_blend`` the values of every such layer of a model but the first to
     run become ``(1 - lam) v + lam v_first`` (``lam`` the layer's ``vmix``, ``v_first`` the first such
-    layer's values of the same token); the blended values are what is cached.  With ``head_gate`` head
+    layer's values of the same token); the blended values are what is cached; ``value_blend: "source"`` marks a layer that
+    only gives its values away and has no ``vmix``.  With ``head_gate`` head
     ``h``'s output is multiplied by ``sigmoid(W_g x)_h``, one number per head.  Scores, weights and sums
     are fp32 for either dtype.
 
@@ -199,7 +200,11 @@ class ChunkAttention(ProjectedMixer):
         self.chunk = int(g("chunk")) if g("chunk") else None
         self.qk_norm = bool(g("qk_norm", False))
         self.eps = float(g("eps", 0.0))
-        self.value_blend = bool(g("value_blend", False))
+        blend = g("value_blend", False)
+        if blend not in (False, True, "source"):
+            raise ValueError(f"value_blend is true, false or 'source', not {blend!r}")
+        self.value_blend = blend is True            # takes ``vmix`` and blends (unless it is the first to run)
+        self.value_source = bool(blend)             # may leave its values for the layers behind it
         self.head_gate = bool(g("head_gate", False))
         if self.nq % self.nkv:
             raise ValueError(f"{self.nq} query heads cannot share {self.nkv} key/value heads")
@@ -263,12 +268,14 @@ class ChunkAttention(ProjectedMixer):
         nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
         rot, freq = _half_rotation(position, d)
         v_other = None
-        if self.value_blend:
+        if self.value_source:
             # the first blending layer to run in a step leaves its values for the others
             values = proj[:, self.v_off:self.v_off + nkv * dv]
             first = ctx.scratch.get("value_blend_source")
             if first is None:
                 ctx.scratch["value_blend_source"] = values
+            elif not self.value_blend:
+                raise ValueError("a layer that only gives its values away runs before the blending ones")
             elif first.shape != values.shape:
                 raise ValueError(f"blended values of {tuple(values.shape)} and a first layer's of {tuple(first.shape)}")
             else:

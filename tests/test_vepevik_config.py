@@ -31,6 +31,13 @@ def test_names_and_shapes_fit_a_checkpoint(which):
     # the ranks of the low-rank products are the checkpoint's: any rank fits, another shape does not
     other = random_state(CONFIGS[which], seed=1, ranks=(RANKS[which][0] + 2, RANKS[which][1] + 1))
     check_names(model, {n: tuple(t.shape) for n, t in other.items()})
+    # the first blending layer's factor is never used: a checkpoint may carry it or not; the others' are needed
+    blending = [f"l{i}.mix.vmix" for i, l in enumerate(CONFIGS[which]["layers"]) if l["mixer"].get("v_mix")]
+    if blending:
+        check_names(model, {n: tuple(t.shape) for n, t in state.items() if n != blending[0]})
+    for name in blending[1:]:
+        with pytest.raises(Exception, match="missing"):
+            check_names(model, {n: tuple(t.shape) for n, t in state.items() if n != name})
     broken = {n: tuple(t.shape) for n, t in state.items()}
     broken["embed"] = broken["embed"][::-1]
     del broken["final.norm"]
