@@ -487,16 +487,20 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
 
 // ------------------------------------------------------------------------------------------
 // gated delta rule.  The columns of a head's state S [dk, dv] evolve independently under the same
-// transition, so a warp owns DELTA_NC columns: lane l keeps rows l, l + 32, ... of each in registers.
-// Per token and column: sg = g * s; r = sg . k; p = sg . q; u = beta (v - r); s = sg + k u;
-// o = p + u (k . q), which is S^T q after the write.  The two dot products of all the warp's columns
-// are reduced over the lanes together.  Tokens are staged in groups of DELTA_L: the block's warps make
-// q and k unit vectors, compute g, beta and k . q, and leave them in shared memory for the walk.
+// transition.  A warp owns DELTA_NC columns and DELTA_PARTS lanes share a column: lane (part, c) keeps R rows
+// of column c in registers, in groups of four consecutive rows dealt out to the parts in turn (group
+// part + DELTA_PARTS * i), so that a part reads its q, k and g as 16-byte words that lie side by side with
+// the other parts'.  Per token and column: sg = g * s; r = sg . k; p = sg . q; u = beta (v - r);
+// s = sg + k u; o = p + u (k . q), which is S^T q after the write.  The two dot products are summed over
+// the column's lanes by three exchanges, in an order that depends on nothing but the sizes.  Tokens are staged
+// in groups of DELTA_L = DELTA_W, one per warp: the warp makes q and k unit vectors, computes g, beta and k . q,
+// and leaves them in shared memory (rows padded to 8 R with k = q = 0, g = 1) for the walk.
 // A block has DELTA_W warps, so it owns DELTA_W * DELTA_NC value columns of one head of one request.
 // state row of a request: [taps-1][C] convolution inputs (oldest first), then S [heads][dk][dv].
 // ------------------------------------------------------------------------------------------
-#define DELTA_L 16
+#define DELTA_L 8   // tokens per group: one per warp
 #define DELTA_NC 4
+#define DELTA_PARTS 8
 #define DELTA_W 8
 #define DELTA_COLS (DELTA_NC * DELTA_W)
 
@@ -510,42 +514,75 @@ delta_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
                   const int* __restrict__ state_slot, float* __restrict__ o, int o_stride, int heads, int kv_heads,
                   int dk, int dv, const T* __restrict__ xin, int xin_stride, int C, int taps) {
   mi_pdl_enter();
-  extern __shared__ float dsm[];
-  float* ks = dsm;                       // [DELTA_L][dk]
-  float* qs = ks + DELTA_L * dk;         // [DELTA_L][dk]
-  float* gs = qs + DELTA_L * dk;         // [DELTA_L][dk]
-  float* vs = gs + DELTA_L * dk;         // [DELTA_L][DELTA_COLS]
+  constexpr int DKP = DELTA_PARTS * R;   // rows of a staged token, padded
+  constexpr int RS = DKP / 32;           // rows a lane stages per token
+  constexpr int NG = R / 4;              // groups of four rows per lane
+  extern __shared__ __align__(16) float dsm[];
+  float* ks = dsm;                       // [DELTA_L][DKP]
+  float* qs = ks + DELTA_L * DKP;        // [DELTA_L][DKP]
+  float* gs = qs + DELTA_L * DKP;        // [DELTA_L][DKP]
+  float* vs = gs + DELTA_L * DKP;        // [DELTA_L][DELTA_COLS]
   float* bs = vs + DELTA_L * DELTA_COLS; // [DELTA_L] beta
   float* kqs = bs + DELTA_L;             // [DELTA_L] k . q
   const int lane = threadIdx.x, warp = threadIdx.y, tid = warp * 32 + lane;
+  const int part = lane / DELTA_NC, col = lane % DELTA_NC;
   const int head = blockIdx.y, req = blockIdx.z;
   const int kvh = head / (heads / kv_heads);
   const int len = q_len[req], row0 = q_start[req];
   float* st = state + (size_t)state_slot[req] * state_stride;
   float* S = st + s_off + (size_t)head * dk * dv;
-  const int j0 = blockIdx.x * DELTA_COLS + warp * DELTA_NC;
+  const int j = blockIdx.x * DELTA_COLS + warp * DELTA_NC + col;   // this lane's column
   const float A = expf(a_log[head]);
-  float s[R][DELTA_NC];
+  float s[R];
 #pragma unroll
-  for (int i = 0; i < R; ++i)
+  for (int i = 0; i < NG; ++i)
 #pragma unroll
-    for (int c = 0; c < DELTA_NC; ++c) {
-      const int kk = lane + 32 * i, j = j0 + c;
-      s[i][c] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
+    for (int e = 0; e < 4; ++e) {
+      const int kk = 4 * (part + DELTA_PARTS * i) + e;
+      s[4 * i + e] = (kk < dk && j < dv) ? S[(size_t)kk * dv + j] : 0.f;
     }
+  // Warp w stages token w of a group.  What it needs from global memory (its token's k, q, pre-activations of
+  // the decay, beta and the block's values) is fetched into registers one group ahead, before the walk
+  // over the group at hand, so that the walk hides the fetch.
+  // (kept as loaded: a conversion would wait for the load where it is issued)
+  float dtb[RS], pz[RS];
+  T pk[RS], pq_[RS], pb = T(0.f), pv = T(0.f);
+#pragma unroll
+  for (int i = 0; i < RS; ++i) {
+    const int kk = lane + 32 * i;
+    dtb[i] = kk < dk ? dt_bias[head * dk + kk] : 0.f;
+    pk[i] = pq_[i] = T(0.f);
+    pz[i] = 0.f;
+  }
+  const int jj = blockIdx.x * DELTA_COLS + lane;   // the column whose value this lane stages
+  auto fetch = [&](int t) {
+    if (t >= len) return;
+    const size_t m = (size_t)(row0 + t);
+    const T* kr = k + m * stride + kvh * dk;
+    const T* qr = q + m * stride + kvh * dk;
+#pragma unroll
+    for (int i = 0; i < RS; ++i) {
+      const int kk = lane + 32 * i;
+      if (kk < dk) {
+        pk[i] = kr[kk];
+        pq_[i] = qr[kk];
+        pz[i] = z[m * z_stride + head * dk + kk];
+      }
+    }
+    pb = b[m * b_stride + head];
+    if (jj < dv) pv = v[m * stride + head * dv + jj];
+  };
+  fetch(warp);
   for (int t0 = 0; t0 < len; t0 += DELTA_L) {
     const int n = min(DELTA_L, len - t0);
     __syncthreads();   // the group before is consumed
-    for (int l = warp; l < n; l += DELTA_W) {
-      const size_t m = (size_t)(row0 + t0 + l);
-      const T* kr = k + m * stride + kvh * dk;
-      const T* qr = q + m * stride + kvh * dk;
-      float kv_[R], qv_[R], ssk = 0.f, ssq = 0.f;
+    if (warp < n) {
+      const int l = warp;
+      float kv_[RS], qv_[RS], ssk = 0.f, ssq = 0.f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int kk = lane + 32 * i;
-        kv_[i] = kk < dk ? mi_to_float(kr[kk]) : 0.f;
-        qv_[i] = kk < dk ? mi_to_float(qr[kk]) : 0.f;
+      for (int i = 0; i < RS; ++i) {
+        kv_[i] = mi_to_float(pk[i]);
+        qv_[i] = mi_to_float(pq_[i]);
         ssk = fmaf(kv_[i], kv_[i], ssk);
         ssq = fmaf(qv_[i], qv_[i], ssq);
       }
@@ -554,79 +591,70 @@ delta_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __r
       const float mk = 1.f / sqrtf(ssk + unit_eps), mq = q_scale / sqrtf(ssq + unit_eps);
       float kq = 0.f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
+      for (int i = 0; i < RS; ++i) {
         const int kk = lane + 32 * i;
+        float kn = 0.f, qn = 0.f, g = 1.f;
         if (kk < dk) {
-          const float kn = kv_[i] * mk, qn = qv_[i] * mq;
-          ks[l * dk + kk] = kn;
-          qs[l * dk + kk] = qn;
-          kq = fmaf(kn, qn, kq);
-          const float dt = mi_softplus(z[m * z_stride + head * dk + kk] + dt_bias[head * dk + kk]);
-          gs[l * dk + kk] = expf(-A * dt);
+          kn = kv_[i] * mk;
+          qn = qv_[i] * mq;
+          g = expf(-A * mi_softplus(pz[i] + dtb[i]));
         }
+        ks[l * DKP + kk] = kn;
+        qs[l * DKP + kk] = qn;
+        gs[l * DKP + kk] = g;
+        kq = fmaf(kn, qn, kq);
       }
       kq = mi_warp_sum(kq);
       if (lane == 0) {
         kqs[l] = kq;
-        bs[l] = mi_sigmoid(mi_to_float(b[m * b_stride + head]));
+        bs[l] = mi_sigmoid(mi_to_float(pb));
       }
-      const int jj = blockIdx.x * DELTA_COLS + lane;
-      vs[l * DELTA_COLS + lane] = jj < dv ? mi_to_float(v[m * stride + head * dv + jj]) : 0.f;
+      vs[l * DELTA_COLS + lane] = jj < dv ? mi_to_float(pv) : 0.f;
     }
     __syncthreads();
+    fetch(t0 + DELTA_L + warp);
     for (int l = 0; l < n; ++l) {
-      float r[DELTA_NC], pq[DELTA_NC];
-#pragma unroll
-      for (int c = 0; c < DELTA_NC; ++c) r[c] = pq[c] = 0.f;
       float kreg[R];
+      float r0 = 0.f, r1 = 0.f, p0 = 0.f, p1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        const int kk = lane + 32 * i;
-        const bool in = kk < dk;
-        const float g = in ? gs[l * dk + kk] : 1.f, qn = in ? qs[l * dk + kk] : 0.f;
-        kreg[i] = in ? ks[l * dk + kk] : 0.f;
-#pragma unroll
-        for (int c = 0; c < DELTA_NC; ++c) {
-          s[i][c] *= g;
-          r[c] = fmaf(s[i][c], kreg[i], r[c]);
-          pq[c] = fmaf(s[i][c], qn, pq[c]);
-        }
+      for (int i = 0; i < NG; ++i) {
+        const int at = l * DKP + 4 * (part + DELTA_PARTS * i);
+        const float4 g4 = *reinterpret_cast<const float4*>(gs + at);
+        const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + at);
+        float* si = s + 4 * i;
+        float* ki = kreg + 4 * i;
+        ki[0] = k4.x; ki[1] = k4.y; ki[2] = k4.z; ki[3] = k4.w;
+        si[0] *= g4.x; si[1] *= g4.y; si[2] *= g4.z; si[3] *= g4.w;
+        r0 = fmaf(si[0], k4.x, r0); r1 = fmaf(si[1], k4.y, r1);
+        r0 = fmaf(si[2], k4.z, r0); r1 = fmaf(si[3], k4.w, r1);
+        p0 = fmaf(si[0], q4.x, p0); p1 = fmaf(si[1], q4.y, p1);
+        p0 = fmaf(si[2], q4.z, p0); p1 = fmaf(si[3], q4.w, p1);
       }
+      float r = r0 + r1, pq = p0 + p1;
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1)
-#pragma unroll
-        for (int c = 0; c < DELTA_NC; ++c) {
-          r[c] += __shfl_xor_sync(0xffffffffu, r[c], off);
-          pq[c] += __shfl_xor_sync(0xffffffffu, pq[c], off);
-        }
-      const float beta = bs[l], kq = kqs[l];
-      float u[DELTA_NC];
-#pragma unroll
-      for (int c = 0; c < DELTA_NC; ++c) u[c] = beta * (vs[l * DELTA_COLS + warp * DELTA_NC + c] - r[c]);
-#pragma unroll
-      for (int i = 0; i < R; ++i)
-#pragma unroll
-        for (int c = 0; c < DELTA_NC; ++c) s[i][c] = fmaf(kreg[i], u[c], s[i][c]);
-      if (lane < DELTA_NC && j0 + lane < dv) {
-        float ov = 0.f;
-#pragma unroll
-        for (int c = 0; c < DELTA_NC; ++c)
-          if (c == lane) ov = fmaf(u[c], kq, pq[c]);
-        o[(size_t)(row0 + t0 + l) * o_stride + head * dv + j0 + lane] = ov;
+      for (int off = DELTA_NC; off < 32; off <<= 1) {
+        r += __shfl_xor_sync(0xffffffffu, r, off);
+        pq += __shfl_xor_sync(0xffffffffu, pq, off);
       }
+      const float u = bs[l] * (vs[l * DELTA_COLS + warp * DELTA_NC + col] - r);
+#pragma unroll
+      for (int i = 0; i < R; ++i) s[i] = fmaf(kreg[i], u, s[i]);
+      if (part == 0 && j < dv) o[(size_t)(row0 + t0 + l) * o_stride + head * dv + j] = fmaf(u, kqs[l], pq);
     }
   }
 #pragma unroll
-  for (int i = 0; i < R; ++i)
+  for (int i = 0; i < NG; ++i)
 #pragma unroll
-    for (int c = 0; c < DELTA_NC; ++c) {
-      const int kk = lane + 32 * i, j = j0 + c;
-      if (kk < dk && j < dv) S[(size_t)kk * dv + j] = s[i][c];
+    for (int e = 0; e < 4; ++e) {
+      const int kk = 4 * (part + DELTA_PARTS * i) + e;
+      if (kk < dk && j < dv) S[(size_t)kk * dv + j] = s[4 * i + e];
     }
-  // the convolution's next tail (one block per request does it): the last taps-1 of (old tail, this
-  // portion's inputs); the convolution itself ran before this kernel
-  if (taps > 1 && blockIdx.x == 0 && blockIdx.y == 0) {
-    for (int c = tid; c < C; c += 32 * DELTA_W) {
+  // the convolution's next tail (the request's blocks share its channels): the last taps-1 of (old tail,
+  // this portion's inputs); the convolution itself ran before this kernel and nothing else reads the tail here
+  if (taps > 1) {
+    const int n_blocks = gridDim.x * gridDim.y, block_id = blockIdx.y * gridDim.x + blockIdx.x;
+    for (int c = block_id * 32 * DELTA_W + tid; c < C; c += n_blocks * 32 * DELTA_W) {
       float keep[MAX_TAPS];
 #pragma unroll
       for (int j = 0; j < MAX_TAPS - 1; ++j) {
@@ -655,7 +683,8 @@ extern "C" int mi_delta_scan(const void* q, const void* k, const void* v, int st
   if (heads > 65535 || n_requests > 65535) MI_REFUSE("delta: too many heads or requests for one launch");
   if (taps < 1 || taps > MAX_TAPS) MI_REFUSE("delta: %d taps (1 to %d are taken)", taps, MAX_TAPS);
   dim3 grid((dv + DELTA_COLS - 1) / DELTA_COLS, heads, n_requests), block(32, DELTA_W);
-  const size_t smem = ((size_t)3 * DELTA_L * dk + DELTA_L * DELTA_COLS + 2 * DELTA_L) * sizeof(float);
+  const int dkp = dk <= 32 ? 32 : dk <= 64 ? 64 : dk <= 128 ? 128 : 256;   // DELTA_PARTS * R of the instance below
+  const size_t smem = ((size_t)3 * DELTA_L * dkp + DELTA_L * DELTA_COLS + 2 * DELTA_L) * sizeof(float);
 #define MI_GO(T, R)                                                                                                  \
   do {                                                                                                               \
     auto kern = delta_scan_kernel<T, R>;                                                                             \
@@ -669,10 +698,10 @@ extern "C" int mi_delta_scan(const void* q, const void* k, const void* v, int st
   } while (0)
 #define MI_GO_R(T)                  \
   do {                              \
-    if (dk <= 32) MI_GO(T, 1);      \
-    else if (dk <= 64) MI_GO(T, 2); \
-    else if (dk <= 128) MI_GO(T, 4);\
-    else MI_GO(T, 8);               \
+    if (dk <= 32) MI_GO(T, 4);       \
+    else if (dk <= 64) MI_GO(T, 8);  \
+    else if (dk <= 128) MI_GO(T, 16);\
+    else MI_GO(T, 32);               \
   } while (0)
   if (dtype == MI_DTYPE_F32) MI_GO_R(float);
   else if (dtype == MI_DTYPE_BF16) MI_GO_R(bf16);
