@@ -237,7 +237,7 @@ def ctx_for(q_lens, slots):
 
 
 @pytest.mark.parametrize("d,dv,rot,norm", [(24, 16, 8, True), (10, 14, 10, True), (64, 64, 64, False), (7, 3, 2, True),
-                                           (128, 32, 64, True), (20, 28, 0, True)])
+                                           (128, 48, 32, True), (20, 28, 0, True)])
 def test_head_norm_half_rotation_and_value_blend(d, dv, rot, norm):
     """RMS norm over the head with a gain shared by the heads, then the rotation of pairs (i, i + rot/2)
     on the first ``rot`` dimensions, then a factor; values blended with another layer's; all in place,
@@ -329,7 +329,7 @@ DELTA_LONG = ({0: 200, 1: 37}, [(130, 30), (1, 0), (69, 7)])
 @pytest.mark.parametrize("heads,kvh,dk,dv,taps,dtype,bound,plan", [
     (4, 2, 12, 20, 3, torch.float32, 2e-5, DELTA_SHORT), (2, 2, 32, 8, 2, torch.float32, 2e-5, DELTA_SHORT),
     (3, 1, 7, 5, 1, torch.float32, 2e-5, DELTA_SHORT), (2, 2, 24, 36, 5, torch.float32, 2e-5, DELTA_LONG),
-    (6, 6, 64, 64, 4, torch.bfloat16, 3e-2, DELTA_LONG), (2, 1, 128, 40, 4, torch.bfloat16, 3e-2, DELTA_SHORT),
+    (6, 3, 64, 48, 4, torch.bfloat16, 3e-2, DELTA_LONG), (2, 1, 128, 40, 4, torch.bfloat16, 3e-2, DELTA_SHORT),
     (1, 1, 200, 33, 2, torch.float32, 2e-5, DELTA_SHORT)])
 def test_delta_rule_carries_state_and_convolution_tail(heads, kvh, dk, dv, taps, dtype, bound, plan):
     """Convolution tail and matrix state through portions of 1, 2 and more tokens, two requests in one
@@ -389,7 +389,7 @@ def test_delta_rule_carries_state_and_convolution_tail(heads, kvh, dk, dv, taps,
 
 
 @pytest.mark.parametrize("E,top,ff,H,M,groups,scale", [
-    (6, 2, 20, 40, 33, (3, 2), 1.5), (8, 2, 24, 48, 70, (2, 1), 2.5), (5, 1, 12, 40, 5, None, 2.0),
+    (6, 2, 20, 40, 33, (3, 2), 1.5), (10, 2, 24, 48, 70, (5, 1), 2.5), (5, 1, 12, 40, 5, None, 2.0),
     (4, 4, 16, 36, 9, None, 1.0), (8, 3, 8, 40, 200, (4, 2), 0.7), (3, 2, 10, 36, 7, (3, 3), 1.0),
     (64, 4, 16, 64, 50, (8, 3), 1.0), (12, 6, 72, 64, 130, (2, 1), 1.0)])
 @pytest.mark.parametrize("dtype,bound", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
