@@ -247,7 +247,7 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
                                           c_int, c_int, c_void_p]
     lib.mi_rglru_chunked_scratch.argtypes = [c_int, c_int, c_int]
     lib.mi_rglru_chunked_scratch.restype = ll
-    lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
+    lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
     lib.mi_delta_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -301,7 +301,7 @@ def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
     lib.mi_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_float, c_float,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_void_p]
+                                          c_void_p, c_int, c_int, c_void_p]
 
 
 def _sig_attention_rows(lib: ctypes.CDLL) -> None:
@@ -1414,8 +1414,10 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor 
     for t in (q, k, v) + ((z,) if z is not None else ()):
         _cols(t, "gla")
     M = q.shape[0]
-    if not (q.stride(0) == k.stride(0) == v.stride(0)) or not (q.dtype == k.dtype == v.dtype):
-        raise KernelError("gla: q, k and v must be column ranges of one packed projection")
+    if q.stride(0) != k.stride(0) or q.dtype != k.dtype:
+        raise KernelError("gla: q and k must be column ranges of one matrix")
+    if q.dtype != v.dtype and (q.dtype, v.dtype) != (torch.float32, torch.bfloat16):
+        raise KernelError("gla: q and k have the values' dtype, or are fp32 beside bfloat16 values")
     if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv:
         raise KernelError("gla: q, k must be [M, heads * dk] and v [M, heads * dv]")
     if head_decay is None and z is None:
@@ -1431,7 +1433,7 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor 
     lib = _lib("recurrent")
     longest = _max_q_len(ctx)
     n_chunks, scratch = 1, None
-    if q.dtype == torch.bfloat16 and longest > GLA_CHUNK:
+    if v.dtype == torch.bfloat16 and longest > GLA_CHUNK:
         # long portions: chunks side by side, two launches (the float32 path keeps the plain walk, whose
         # sums do not depend on where a portion starts)
         global launch_count
@@ -1439,11 +1441,12 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor 
         scratch = torch.empty(lib.mi_gla_chunked_scratch(ctx.n_requests, n_chunks, heads, dk, dv), dtype=torch.float32,
                               device=q.device)
         launch_count += 1
-    rc = lib.mi_gla_scan(_ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(z), z.stride(0) if z is not None else 0,
+    rc = lib.mi_gla_scan(_ptr(q), _ptr(k), q.stride(0), _code(q.dtype), _ptr(v), v.stride(0), _ptr(z),
+                         z.stride(0) if z is not None else 0,
                          _ptr(z_bias), 1.0 / float(tau),
                          float(q_scale), _ptr(state), stride, _ptr(ctx.q_start), _ptr(ctx.q_len),
                          _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _ptr(scratch),
-                         n_chunks, GLA_CHUNK, _ptr(head_decay), _code(q.dtype), _stream())
+                         n_chunks, GLA_CHUNK, _ptr(head_decay), _code(v.dtype), _stream())
     _finish(lib, rc, "gla")
     return o
 
@@ -1763,7 +1766,7 @@ def qk_bias_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int,
                        q_bias: torch.Tensor | None, k_bias: torch.Tensor | None, q_gain: torch.Tensor | None,
                        k_gain: torch.Tensor | None, eps: float, values_are_keys: bool,
                        slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
-                       vcache: torch.Tensor | None = None) -> None:
+                       vcache: torch.Tensor | None = None, qk_out: torch.Tensor | None = None) -> None:
     """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
     ``k_off``, ``nkv`` heads of ``d``): add the biases (fp32 ``[heads * d]``), then give every head an
     RMS norm with the gain shared by the heads (fp32 ``[d]``; None: no norm); q and k are written back
@@ -1802,7 +1805,7 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
                        freq: torch.Tensor | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
                        v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
                        slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
-                       vcache: torch.Tensor | None = None) -> None:
+                       vcache: torch.Tensor | None = None, qk_out: torch.Tensor | None = None) -> None:
     """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
     ``k_off``, ``nkv`` heads of ``d``; v at ``v_off``, ``nkv`` heads of ``dv``, or ``v_off`` None: no values
     here): q and k get an RMS norm over the head with the gain shared by the heads (fp32 ``[d]``; None:
@@ -1810,8 +1813,9 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
     ``[rot / 2]``; the angle in double precision), then the factors ``q_scale`` / ``k_scale``; both are
     written back.  With ``v_other`` (``[M, nkv * dv]``) and ``blend`` (fp32, one element) the values
     become ``(1 - blend) v + blend v_other`` and are written back too.  With caches, k and v are stored
-    at ``slots``."""
-    _cuda(packed, q_gain, k_gain, positions, freq, v_other, blend, slots, kcache, vcache)
+    at ``slots``.  With ``qk_out`` (fp32 ``[M, (nq + nkv) * d]``, queries first) the finished q and k go there
+    unrounded and their packed columns stay as they were: for a recurrence that takes them in fp32."""
+    _cuda(packed, q_gain, k_gain, positions, freq, v_other, blend, slots, kcache, vcache, qk_out)
     _cols(packed, "qk_prepare")
     M, width = packed.shape
     has_v = v_off is not None
@@ -1841,12 +1845,16 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
                     or not c.is_contiguous()):
                 raise KernelError("qk_prepare: caches must be contiguous [pages, nkv, page_size, size] in the packed dtype")
         page_size = int(kcache.shape[2])
+    if qk_out is not None and (qk_out.dtype != torch.float32 or qk_out.shape != (M, (nq + nkv) * d)
+                               or qk_out.stride(1) != 1):
+        raise KernelError("qk_prepare: qk_out must be fp32 [M, (nq + nkv) * d]")
     lib = _lib("qk_prepare")
     rc = lib.mi_qk_norm_rope_store(_ptr(packed), packed.stride(0), q_off, k_off, v_off if has_v else -1, M, nq, nkv, d,
                                    dv, _ptr(q_gain), _ptr(k_gain), float(eps), int(rot), _ptr(positions), _ptr(freq),
                                    float(q_scale), float(k_scale), _ptr(v_other),
                                    v_other.stride(0) if v_other is not None else 0, _ptr(blend), _ptr(slots),
                                    _ptr(kcache), _ptr(vcache if has_v else None), page_size, 1 if writes else 0,
+                                   _ptr(qk_out), qk_out.stride(0) if qk_out is not None else 0,
                                    _code(packed.dtype), _stream())
     _finish(lib, rc, "qk_prepare")
 

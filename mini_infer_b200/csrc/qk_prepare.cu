@@ -236,7 +236,10 @@ qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
                           int rot, const int* __restrict__ positions, const double* __restrict__ freq, float q_scale,
                           float k_scale, const T* __restrict__ v_other, int v_other_stride,
                           const float* __restrict__ lam_ptr, const int* __restrict__ slots, T* __restrict__ kcache,
-                          T* __restrict__ vcache, int page_size, int writes) {
+                          T* __restrict__ vcache, int page_size, int writes, float* __restrict__ qk_out,
+                          int qk_out_stride) {
+  // qk_out [M, (nq + nkv) * d] fp32: the finished queries and keys go there unrounded (for a recurrence
+  // that reads them in fp32) and the packed rows keep what the projection left.
   mi_pdl_enter();
   extern __shared__ float rope_sm[];
   const int half = rot >> 1;
@@ -308,7 +311,8 @@ qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
         y = k < half ? y1 : y2;
       }
       const T out = mi_from_float<T>(y * post);
-      x[k] = out;
+      if (qk_out) qk_out[(size_t)t * qk_out_stride + (size_t)h * d + k] = y * post;
+      else x[k] = out;
       if (kdst) kdst[mi_swizzled(k, offset, mk, EPC)] = out;
     }
     __syncwarp();                      // the warp's buffer is free for its next head
@@ -319,9 +323,10 @@ extern "C" int mi_qk_norm_rope_store(void* packed, int stride, int q_off, int k_
                                      int d, int dv, const float* q_gain, const float* k_gain, float eps, int rot,
                                      const int* positions, const double* freq, float q_scale, float k_scale,
                                      const void* v_other, int v_other_stride, const float* lam, const int* slots,
-                                     void* kcache, void* vcache, int page_size, int writes, int dtype,
-                                     cudaStream_t stream) {
+                                     void* kcache, void* vcache, int page_size, int writes, float* qk_out,
+                                     int qk_out_stride, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
+  if (qk_out && qk_out_stride < (nq + nkv) * d) MI_REFUSE("qk_prepare: fp32 rows of %d for %d heads of %d", qk_out_stride, nq + nkv, d);
   if (d <= 0 || d > ROPE_MAX_D || dv < 0) MI_REFUSE("qk_prepare: head size %d must lie in [1, %d]", d, ROPE_MAX_D);
   if (rot < 0 || rot > d || (rot & 1)) MI_REFUSE("qk_prepare: %d rotated dimensions of %d", rot, d);
   if (rot > 0 && (!positions || !freq)) MI_REFUSE("qk_prepare: a rotation needs positions and frequencies");
@@ -334,7 +339,7 @@ extern "C" int mi_qk_norm_rope_store(void* packed, int stride, int q_off, int k_
 #define MI_GO(T)                                                                                                       \
   MI_LAUNCH((qk_norm_rope_store_kernel<T>), grid, 128, smem, stream, (T*)packed, stride, q_off, k_off, v_off, nq, nkv, \
             d, dv, q_gain, k_gain, eps, rot, positions, freq, q_scale, k_scale, (const T*)v_other, v_other_stride,    \
-            lam, slots, (T*)kcache, (T*)vcache, page_size, writes)
+            lam, slots, (T*)kcache, (T*)vcache, page_size, writes, qk_out, qk_out_stride)
   if (dtype == MI_DTYPE_F32) MI_GO(float);
   else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
   else MI_REFUSE("qk_prepare: unknown dtype %d", dtype);

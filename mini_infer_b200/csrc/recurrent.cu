@@ -307,8 +307,9 @@ extern "C" int mi_rglru_scan_chunked(const float* gates, int M, int bw, const fl
 #define GLA_R 8
 #define GLA_L 16
 
-template <typename T, int MAXT>
-__global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, int stride,
+template <typename TQ, typename T, int MAXT>
+__global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q, const TQ* __restrict__ k, int qk_stride,
+                                const T* __restrict__ v, int stride,
                                 const float* __restrict__ z, int z_stride, const float* __restrict__ z_bias,
                                 float inv_tau, float q_scale, float* __restrict__ state, long long state_stride,
                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
@@ -316,6 +317,7 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
                                 int heads, int dk, int dv, int pass, int chunk_len, int n_chunks,
                                 float* __restrict__ scratch, const float* __restrict__ head_decay) {
   // head_decay [heads]: one fixed decay per head in the place of alpha (z is then not read).
+  // q and k may be fp32 rows of their own (what a rotation left in fp32) beside bfloat16 values.
   // pass 0: the whole portion, from and into the state.  Long portions run as chunks side by side:
   // pass 1 folds every chunk into (A, B) with S_end = diag(A) S_begin + B (and saves the state the
   // portion starts from), pass 2 walks the chunks before its own to get S_begin and then its own
@@ -375,8 +377,8 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const T* __restrict__ q,
       if (idx < n * dk) {
         const int l = idx / dk, kk = idx - l * dk;
         const size_t m = (size_t)(row0 + t0 + l);
-        pq[i] = mi_to_float(q[m * stride + head * dk + kk]);
-        pk[i] = mi_to_float(k[m * stride + head * dk + kk]);
+        pq[i] = mi_to_float(q[m * qk_stride + head * dk + kk]);
+        pk[i] = mi_to_float(k[m * qk_stride + head * dk + kk]);
         pz[i] = head_decay ? 0.f : z[m * z_stride + head * dk + kk];
       }
     }
@@ -452,7 +454,8 @@ extern "C" long long mi_gla_chunked_scratch(int n_requests, int n_chunks, int he
   return (long long)n_requests * n_chunks * heads * unit + (long long)n_requests * heads * dk * dv;
 }
 
-extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stride, const float* z, int z_stride,
+extern "C" int mi_gla_scan(const void* q, const void* k, int qk_stride, int qk_dtype, const void* v, int stride,
+                           const float* z, int z_stride,
                            const float* z_bias, float inv_tau, float q_scale, float* state, long long state_stride,
                            const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
                            int n_requests, int heads, int dk, int dv, float* scratch, int n_chunks, int chunk_len,
@@ -466,21 +469,22 @@ extern "C" int mi_gla_scan(const void* q, const void* k, const void* v, int stri
   const int KP = max(4, (dk + GLA_R - 1) / GLA_R);     // at least 128 threads: they also stage the inputs
   dim3 grid((dv + 31) / 32, heads, n_requests * n_chunks), block(32, KP);
   const size_t smem = ((size_t)3 * GLA_L * dk + GLA_L * 32 + (size_t)GLA_L * KP * 32) * sizeof(float);
-#define MI_GO(T)                                                                                          \
+#define MI_GO(TQ, T)                                                                                      \
   do {                                                                                                    \
-    auto kern = KP <= 16 ? gla_scan_kernel<T, 512> : gla_scan_kernel<T, 1024>;                            \
+    auto kern = KP <= 16 ? gla_scan_kernel<TQ, T, 512> : gla_scan_kernel<TQ, T, 1024>;                    \
     if (smem > 48 * 1024) {                                                                               \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                                \
     }                                                                                                     \
     for (int pass = n_chunks > 1 ? 1 : 0; pass <= (n_chunks > 1 ? 2 : 0); ++pass)                         \
-      MI_LAUNCH(kern, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, stride, z, z_stride, \
+      MI_LAUNCH(kern, grid, block, smem, stream, (const TQ*)q, (const TQ*)k, qk_stride, (const T*)v, stride, z, z_stride, \
                 z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, \
                 dk, dv, pass, chunk_len, n_chunks, scratch, head_decay);                                   \
   } while (0)
-  if (dtype == MI_DTYPE_F32) MI_GO(float);
-  else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
-  else MI_REFUSE("gla: unknown dtype %d", dtype);
+  if (dtype == MI_DTYPE_F32 && qk_dtype == MI_DTYPE_F32) MI_GO(float, float);
+  else if (dtype == MI_DTYPE_BF16 && qk_dtype == MI_DTYPE_BF16) MI_GO(bf16, bf16);
+  else if (dtype == MI_DTYPE_BF16 && qk_dtype == MI_DTYPE_F32) MI_GO(float, bf16);
+  else MI_REFUSE("gla: dtypes %d (q, k) and %d (v) are not taken together", qk_dtype, dtype);
 #undef MI_GO
   MI_RETURN_LAUNCH_STATUS();
 }

@@ -408,13 +408,18 @@ class Retention(ProjectedMixer):
     def mix(self, proj, out, out_scale, ctx, cache, position):
         hk, hv = self.heads * self.dk, self.heads * self.dv
         rot, freq = _half_rotation(position, self.dk)
+        q, k = proj[:, self.q_off:self.q_off + hk], proj[:, self.k_off:self.k_off + hk]
         if rot:
+            # what enters the recurrence stays in fp32: the rotated q and k are not rounded to bfloat16 again
+            qk = torch.empty((ctx.n_tokens, 2 * hk), dtype=torch.float32, device=proj.device) \
+                if proj.dtype != torch.float32 else None
             ops.qk_norm_rope_store(proj, self.q_off, self.k_off, None, self.heads, self.heads, self.dk, self.dv,
-                                   rot=rot, positions=ctx.positions, freq=freq)
+                                   rot=rot, positions=ctx.positions, freq=freq, qk_out=qk)
+            if qk is not None:
+                q, k = qk[:, :hk], qk[:, hk:]
         # the keys' factor rides on the queries: o is linear in both
-        o = ops.gla_scan(proj[:, self.q_off:self.q_off + hk], proj[:, self.k_off:self.k_off + hk],
-                         proj[:, self.v_off:self.v_off + hv], None, None, 1.0, self.dk ** -0.5, self.heads, self.dk,
-                         self.dv, cache.state, ctx, head_decay=self.head_decay)
+        o = ops.gla_scan(q, k, proj[:, self.v_off:self.v_off + hv], None, None, 1.0, self.dk ** -0.5, self.heads,
+                         self.dk, self.dv, cache.state, ctx, head_decay=self.head_decay)
         ops.headnorm_gate(o, self.unit_gain, proj[:, self.g_off:self.g_off + hv], out, self.heads, self.dv, self.eps,
                           "silu", out_scale)
 

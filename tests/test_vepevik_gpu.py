@@ -322,6 +322,51 @@ def test_retention_state_and_a_far_key(heads, dk, dv, dtype, portions):
     assert (out.cpu().double() - ref).abs().max() <= 1e-5 * max(1.0, ref.abs().max())
 
 
+@pytest.mark.parametrize("heads,dk,dv,rot,portions", [(2, 24, 40, 8, (1, 150, 1, 2)), (3, 16, 8, 16, (40, 1, 1)),
+                                                     (1, 72, 33, 36, (3, 300))])
+def test_rotated_queries_and_keys_enter_the_recurrence_unrounded(heads, dk, dv, rot, portions):
+    """From bfloat16 projections the rotation leaves q and k in fp32 rows of their own (the packed
+    columns stay as they were) and the scan reads them beside bfloat16 values: against the plain
+    rotation and token loop in float64 the output is as close as fp32 arithmetic gets, which a second
+    rounding of q and k to bfloat16 would miss by a hundred times."""
+    Tn, base = sum(portions), 700.0
+    decay = [0.99, 0.8, 0.95][:heads]
+    hk, hv = heads * dk, heads * dv
+    stride = 2 * hk + hv + 6
+    stride += (-stride) % 8
+    packed = rnd(Tn, stride, seed=60).to(torch.bfloat16)
+    pos = list(range(5000, 5000 + Tn))
+    x = packed.double()
+    q = P.rotate_half_layout(x[:, :hk].reshape(Tn, heads, dk), pos, base, rot)
+    k = P.rotate_half_layout(x[:, hk:2 * hk].reshape(Tn, heads, dk), pos, base, rot)
+    v = x[:, 2 * hk:2 * hk + hv].reshape(Tn, heads, dv)
+    dec = torch.tensor(decay, dtype=torch.float32).double()
+    S = torch.zeros(heads, dk, dv, dtype=torch.float64)
+    want = torch.empty(Tn, heads, dv, dtype=torch.float64)
+    for t in range(Tn):
+        S = dec[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        want[t] = torch.einsum("hkv,hk->hv", S, q[t] * dk ** -0.5)
+    dev = packed.to(DEV)
+    qk = torch.full((Tn, 2 * hk), float("nan"), device=DEV)
+    freq = base ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)
+    ops().qk_norm_rope_store(dev, 0, hk, None, heads, heads, dk, dv, rot=rot,
+                             positions=torch.tensor(pos, dtype=torch.int32, device=DEV), freq=freq.to(DEV), qk_out=qk)
+    assert torch.equal(dev.cpu(), packed)                      # nothing is written back
+    assert (qk[:, :hk].cpu().double().reshape(Tn, heads, dk) - q).abs().max() <= 3e-6 * q.abs().max()
+    assert (qk[:, hk:].cpu().double().reshape(Tn, heads, dk) - k).abs().max() <= 3e-6 * k.abs().max()
+    state = torch.zeros(2, heads, dk, dv, device=DEV)
+    got, t0 = [], 0
+    for n in portions:
+        o = ops().gla_scan(qk[t0:t0 + n, :hk], qk[t0:t0 + n, hk:], dev[t0:t0 + n, 2 * hk:2 * hk + hv], None, None, 1.0,
+                           dk ** -0.5, heads, dk, dv, state, ctx_for([n], [1]),
+                           head_decay=torch.tensor(decay, device=DEV))
+        got.append(o.cpu().double())
+        t0 += n
+    got = torch.cat(got).reshape(Tn, heads, dv)
+    assert (got - want).abs().max() <= 3e-5 * max(1.0, want.abs().max())
+    assert (state[1].cpu().double() - S).abs().max() <= 3e-5 * max(1.0, S.abs().max())
+
+
 DELTA_SHORT = ({0: 23, 1: 9}, [(1, 2), (2, 1), (7, 0), (1, 1), (3, 5), (9, 0)])
 DELTA_LONG = ({0: 200, 1: 37}, [(130, 30), (1, 0), (69, 7)])
 
