@@ -112,4 +112,4 @@ def _load_builtin() -> None:
     if _builtin_loaded:
         return
     _builtin_loaded = True
-    from ..models import lilulix, llama, ruvurax, vepevik  # noqa: F401  (register themselves on import)
+    from ..models import lilulix, llama, ruburax, ruvurax, vepevik  # noqa: F401  (register themselves on import)

@@ -3,7 +3,8 @@
 //   mi_moe_select     from the router logits z = W_r x (fp32, a matrix product): the `top` largest of a token
 //                     (ties: the lower index; optionally among the experts of the best groups only) and
 //                     their weights (the softmax over those alone, or their share of the softmax over all
-//                     experts, times a factor) -> ids [M, top] int32, weights [M, top] fp32
+//                     experts, times a factor, or their sigmoids times a factor, chosen with a correction
+//                     added per expert) -> ids [M, top] int32, weights [M, top] fp32
 //   mi_moe_plan       sorts the M*top (token, choice) entries by expert: perm[pos] = entry, inv[entry] =
 //                     pos, offsets[E + 1], and the list of row tiles (expert, first row, rows) that the
 //                     grouped products walk.  Nothing comes back to the host: the products are launched
@@ -12,7 +13,8 @@
 //   mi_moe_gate_up    act[pos, :] = glu(W_gate[e] x_token, W_up[e] x_token) for the entries of each expert
 //   mi_moe_down       y[pos, :] = W_down[e] act[pos, :]   (fp32)
 //   mi_moe_gather     xs[pos, :] = x[token of pos, :], for steps whose products are a library's grouped product
-//   mi_moe_combine    out[t, :] = T(sum_k weight[t, k] * y[inv[t*top + k], :] + shared[t, :])
+//   mi_moe_combine    out[t, :] = T(sum_k weight[t, k] * y[inv[t*top + k], :] + shared[t, :]), the shared
+//                     expert's row optionally times sigmoid(gate[t])
 //   mi_clamped_glu    the same activation for a dense expert: out = glu(gu[:, :I], gu[:, I:])
 //
 // glu(g, u) = g' * sigmoid(alpha * g') * (u' + offset), g' = min(g, limit), u' = clamp(u, -limit, limit).
@@ -36,29 +38,41 @@ __device__ __forceinline__ float mi_clamped_glu_value(float g, float u, float li
 
 // ------------------------------------------------------------------------------------------ router
 // The logits [M, E] (fp32) come from a matrix product; one warp per token picks the `top` largest
-// (ties: the lower index).  Two ways to weigh them.  all_scores = 0: the softmax over the chosen logits
-// alone.  all_scores = 1: scores are the softmax over all experts; the chosen experts' scores are divided
-// by their sum (+ 1e-20) and multiplied by `scale`.  With n_groups > 1 the experts lie in n_groups equal
-// groups of neighbours, a group counts as its best expert, and only experts of the `keep` best groups
-// (ties: the lower index) can be chosen.
+// choice scores (ties: the lower index).  Three ways to score and weigh.  mode 0: the choice score is
+// the logit, the weights the softmax over the chosen logits alone.  mode 1: scores are the softmax over all
+// experts (the logit orders alike); the chosen experts' scores are divided by their sum (+ 1e-20) and
+// multiplied by `scale`.  mode 2: scores are sigmoid(logit), the choice score adds `correction[e]` (may be
+// absent), the weights are the chosen experts' scores times `scale`, not renormalised.  With n_groups > 1
+// the experts lie in n_groups equal groups of neighbours and only experts of the `keep` best groups (ties:
+// the lower index) can be chosen; a group counts as its best choice score (group_top2 = 0) or as the sum
+// of its two best (group_top2 = 1).
 #define ROUTE_MAX_PER_LANE 8
+#define ROUTE_WARPS 4
 
-__global__ void moe_select_kernel(const float* __restrict__ logits, int stride, int* __restrict__ ids,
-                                  float* __restrict__ weights, int M, int E, int top, int all_scores, int n_groups,
-                                  int keep, float scale) {
+__global__ void __launch_bounds__(32 * ROUTE_WARPS)
+moe_select_kernel(const float* __restrict__ logits, int stride, int* __restrict__ ids,
+                  float* __restrict__ weights, int M, int E, int top, int mode, int n_groups,
+                  int keep, float scale, const float* __restrict__ correction, int group_top2) {
   mi_pdl_enter();
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  __shared__ float choice_sh[ROUTE_WARPS][32 * ROUTE_MAX_PER_LANE];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= M) return;
   const float* z = logits + (size_t)t * stride;
-  float lg[ROUTE_MAX_PER_LANE];
+  float lg[ROUTE_MAX_PER_LANE];       // choice scores; minus infinity: out of the race
+  float sc[ROUTE_MAX_PER_LANE];       // mode 2: the scores that become weights
 #pragma unroll
   for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     lg[i] = e < E ? z[e] : -INFINITY;
+    sc[i] = 0.f;
+    if (mode == 2 && e < E) {
+      sc[i] = 1.f / (1.f + expf(-lg[i]));
+      lg[i] = sc[i] + (correction ? correction[e] : 0.f);
+    }
   }
   float zmax = -INFINITY, zsum = 0.f;
-  if (all_scores) {
+  if (mode == 1) {
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) zmax = fmaxf(zmax, lg[i]);
     zmax = mi_warp_max(zmax);
@@ -68,21 +82,38 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
     zsum = mi_warp_sum(zsum);
   }
   if (n_groups > 1) {
-    // the groups that stay: `keep` times the best group that is still in, by its best logit (the
-    // softmax keeps the order); experts of the others are taken out
+    // group g's score sits with lane g % 32, place g / 32; the groups that stay: `keep` times the
+    // best group that is still in; experts of the others are taken out
     const int per = E / n_groups;
-    unsigned long long kept_lo = 0ull, kept_hi[3] = {0ull, 0ull, 0ull};   // up to 256 groups, one bit each
+    float* mine = choice_sh[warp];
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+      if (lane + 32 * i < E) mine[lane + 32 * i] = lg[i];
+    __syncwarp();
+    float gs[ROUTE_MAX_PER_LANE];
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+      const int g = lane + 32 * i;
+      gs[i] = -INFINITY;
+      if (g < n_groups) {
+        float b1 = -INFINITY, b2 = -INFINITY;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = mine[e];
+          if (v > b1) { b2 = b1; b1 = v; }
+          else if (v > b2) b2 = v;
+        }
+        gs[i] = (group_top2 && per > 1) ? b1 + b2 : b1;
+      }
+    }
+    unsigned kept_mask = 0u;             // bit i: this lane's group lane + 32 i stays
     for (int k = 0; k < keep; ++k) {
       float best = -INFINITY;
       int best_g = 0x7fffffff;
 #pragma unroll
       for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
-        const int e = lane + 32 * i;
-        if (e >= E) continue;
-        const int g = e / per;
-        const bool taken = g < 64 ? (kept_lo >> g) & 1ull : (kept_hi[(g >> 6) - 1] >> (g & 63)) & 1ull;
-        if (!taken && (lg[i] > best || (lg[i] == best && g < best_g))) {
-          best = lg[i];
+        const int g = lane + 32 * i;
+        if (g < n_groups && !((kept_mask >> i) & 1u) && (gs[i] > best || (gs[i] == best && g < best_g))) {
+          best = gs[i];
           best_g = g;
         }
       }
@@ -96,16 +127,14 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
         }
       }
       if (best_g == 0x7fffffff) break;
-      if (best_g < 64) kept_lo |= 1ull << best_g;
-      else kept_hi[(best_g >> 6) - 1] |= 1ull << (best_g & 63);
+      if ((best_g & 31) == lane) kept_mask |= 1u << (best_g >> 5);
     }
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
       const int e = lane + 32 * i;
-      if (e >= E) continue;
-      const int g = e / per;
-      const bool in = g < 64 ? (kept_lo >> g) & 1ull : (kept_hi[(g >> 6) - 1] >> (g & 63)) & 1ull;
-      if (!in) lg[i] = -INFINITY;
+      const int g = e < E ? e / per : 0;
+      const unsigned owner_mask = __shfl_sync(0xffffffffu, kept_mask, g & 31);   // every lane takes part
+      if (e < E && !((owner_mask >> (g >> 5)) & 1u)) lg[i] = -INFINITY;
     }
   }
   float my_val = 0.f, denom = 0.f, first = 0.f;
@@ -130,11 +159,17 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
         best_e = oe;
       }
     }
+    float score = 0.f;
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-      if (best_e == lane + 32 * i) lg[i] = -INFINITY;   // taken
+      if (best_e == lane + 32 * i) {
+        lg[i] = -INFINITY;   // taken
+        score = sc[i];
+      }
     if (k == 0) first = best;
-    const float p = all_scores ? expf(best - zmax) / zsum : expf(best - first);
+    float p;
+    if (mode == 2) p = __shfl_sync(0xffffffffu, score, best_e & 31);
+    else p = mode == 1 ? expf(best - zmax) / zsum : expf(best - first);
     denom += p;
     if (lane == k) {
       my_val = p;
@@ -143,22 +178,25 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int stride, 
   }
   if (lane < top) {
     ids[(size_t)t * top + lane] = my_id;
-    weights[(size_t)t * top + lane] = all_scores ? my_val / (denom + 1e-20f) * scale : my_val / denom;
+    weights[(size_t)t * top + lane] = mode == 2 ? my_val * scale
+                                    : mode == 1 ? my_val / (denom + 1e-20f) * scale : my_val / denom;
   }
 }
 
 extern "C" int mi_moe_select(const float* logits, int stride, int* ids, float* weights, int M, int E, int top,
-                             int all_scores, int n_groups, int keep, float scale, cudaStream_t stream) {
+                             int mode, int n_groups, int keep, float scale, const float* correction,
+                             int group_top2, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (E <= 0 || E > 32 * ROUTE_MAX_PER_LANE) MI_REFUSE("moe: %d experts (1 to %d are taken)", E, 32 * ROUTE_MAX_PER_LANE);
   if (top <= 0 || top > E || top > 32) MI_REFUSE("moe: %d of %d experts per token", top, E);
+  if (mode < 0 || mode > 2) MI_REFUSE("moe: unknown way %d to score the experts", mode);
   if (n_groups > 1) {
     if (E % n_groups) MI_REFUSE("moe: %d experts are no %d equal groups", E, n_groups);
     if (keep <= 0 || keep > n_groups) MI_REFUSE("moe: %d of %d groups kept", keep, n_groups);
     if (keep * (E / n_groups) < top) MI_REFUSE("moe: %d groups of %d experts cannot give %d experts", keep, E / n_groups, top);
   }
-  MI_LAUNCH((moe_select_kernel), (M + 3) / 4, 128, 0, stream, logits, stride, ids, weights, M, E, top, all_scores,
-            n_groups, keep, scale);
+  MI_LAUNCH((moe_select_kernel), (M + ROUTE_WARPS - 1) / ROUTE_WARPS, 32 * ROUTE_WARPS, 0, stream, logits, stride, ids,
+            weights, M, E, top, mode, n_groups, keep, scale, correction, group_top2);
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -603,32 +641,36 @@ extern "C" int mi_moe_gather(const void* x, int x_stride, const int* perm, int t
 template <typename T, typename YT>
 __global__ void moe_combine_kernel(const YT* __restrict__ y, const int* __restrict__ inv,
                                    const float* __restrict__ weights, const T* __restrict__ shared, int shared_stride,
-                                   T* __restrict__ out, int H, int top) {
+                                   T* __restrict__ out, int H, int top, const float* __restrict__ shared_gate,
+                                   int gate_stride) {
   mi_pdl_enter();
   const int t = blockIdx.x;
+  // shared_gate: one fp32 number per token whose sigmoid multiplies the shared expert's output
+  const float sg = (shared && shared_gate) ? 1.f / (1.f + expf(-shared_gate[(size_t)t * gate_stride])) : 1.f;
   for (int c = threadIdx.x; c < H; c += blockDim.x) {
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
       acc = fmaf(weights[(size_t)t * top + k], mi_to_float(y[(size_t)inv[(size_t)t * top + k] * H + c]), acc);
-    if (shared) acc += mi_to_float(shared[(size_t)t * shared_stride + c]);
+    if (shared) acc = fmaf(sg, mi_to_float(shared[(size_t)t * shared_stride + c]), acc);
     out[(size_t)t * H + c] = mi_from_float<T>(acc);
   }
 }
 
 // y_dtype: the experts' outputs are fp32 (own products) or in the compute dtype (a library's grouped product)
 extern "C" int mi_moe_combine(const void* y, int y_dtype, const int* inv, const float* weights, const void* shared,
-                              int shared_stride, void* out, int M, int H, int top, int dtype, cudaStream_t stream) {
+                              int shared_stride, void* out, int M, int H, int top, const float* shared_gate,
+                              int gate_stride, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   if (dtype == MI_DTYPE_F32 && y_dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_combine_kernel<float, float>), M, threads, 0, stream, (const float*)y, inv, weights,
-              (const float*)shared, shared_stride, (float*)out, H, top);
+              (const float*)shared, shared_stride, (float*)out, H, top, shared_gate, gate_stride);
   else if (dtype == MI_DTYPE_BF16 && y_dtype == MI_DTYPE_F32)
     MI_LAUNCH((moe_combine_kernel<bf16, float>), M, threads, 0, stream, (const float*)y, inv, weights,
-              (const bf16*)shared, shared_stride, (bf16*)out, H, top);
+              (const bf16*)shared, shared_stride, (bf16*)out, H, top, shared_gate, gate_stride);
   else if (dtype == MI_DTYPE_BF16 && y_dtype == MI_DTYPE_BF16)
     MI_LAUNCH((moe_combine_kernel<bf16, bf16>), M, threads, 0, stream, (const bf16*)y, inv, weights,
-              (const bf16*)shared, shared_stride, (bf16*)out, H, top);
+              (const bf16*)shared, shared_stride, (bf16*)out, H, top, shared_gate, gate_stride);
   else
     MI_REFUSE("moe: unsupported dtypes %d (activations) and %d (expert outputs)", dtype, y_dtype);
   MI_RETURN_LAUNCH_STATUS();

@@ -249,7 +249,9 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mi_rglru_chunked_scratch.restype = ll
     lib.mi_gla_scan.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float,
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p]
+                                c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.mi_mlstm_gates.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, ll, ll, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mi_delta_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_int, c_float, c_float, c_void_p, ll, ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -257,13 +259,13 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mi_gla_chunked_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mi_gla_chunked_scratch.restype = ll
     lib.mi_headnorm_gate.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                     c_int, c_float, c_int, c_float, c_int, c_void_p]
+                                     c_int, c_float, c_int, c_float, c_int, c_void_p, c_float, c_int, c_void_p]
 
 
 def _sig_moe(lib: ctypes.CDLL) -> None:
     ll = ctypes.c_longlong
     lib.mi_moe_select.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_float, c_void_p]
+                                  c_float, c_void_p, c_int, c_void_p]
     lib.mi_moe_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     lib.mi_moe_tile_rows.argtypes = [c_int]
     lib.mi_moe_tile_rows.restype = c_int
@@ -272,7 +274,7 @@ def _sig_moe(lib: ctypes.CDLL) -> None:
     lib.mi_moe_down.argtypes = [c_void_p, c_void_p, ll, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p]
     lib.mi_moe_combine.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                   c_int, c_void_p]
+                                   c_void_p, c_int, c_int, c_void_p]
     lib.mi_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_clamped_glu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p]
 
@@ -287,6 +289,11 @@ def _sig_stream(lib: ctypes.CDLL) -> None:
     lib.mi_glu_mul_pairs.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mi_embedding_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int,
                                          c_void_p]
+    lib.mi_scaled_norm_add.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_int, c_int,
+                                       c_int, c_void_p]
+    lib.mi_token_gate.argtypes = [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                                  c_int, c_int, c_void_p]
+    lib.mi_scale_f32.argtypes = [c_void_p, ll, c_float, c_void_p]
 
 
 def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
@@ -301,7 +308,7 @@ def _sig_qk_prepare(lib: ctypes.CDLL) -> None:
     lib.mi_qk_norm_rope_store.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_float, c_float,
                                           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_void_p, c_int, c_int, c_void_p]
+                                          c_void_p, c_int, c_void_p, c_int, c_void_p]
 
 
 def _sig_attention_rows(lib: ctypes.CDLL) -> None:
@@ -1252,19 +1259,23 @@ def rope_norm_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int, nq
 _ACT = {"sigmoid": 1, "silu": 2, None: 0}
 
 
-def gate_mul(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, act: str, scale: float = 1.0,
+def gate_mul(x: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, act: str | None, scale: float = 1.0,
              per: int = 1) -> None:
     """``out = x * act(gate) * scale`` element by element; ``x`` and ``out`` ``[M, C]`` (column ranges of
     wider tensors are fine), ``act`` ``"sigmoid"`` or ``"silu"``, fp32 arithmetic.  ``per`` > 1: one gate
-    for every ``per`` neighbouring columns (a gate per head), ``gate`` being ``[M, C / per]``."""
+    for every ``per`` neighbouring columns (a gate per head), ``gate`` being ``[M, C / per]``.  Without a
+    gate (``gate`` and ``act`` None): ``out = x * scale``."""
     _cuda(x, gate, out)
-    for t in (x, gate, out):
+    for t in (x, out) + ((gate,) if gate is not None else ()):
         _cols(t, "gate_mul")
-    if (per <= 0 or x.shape[1] % per or tuple(gate.shape) != (x.shape[0], x.shape[1] // per) or x.shape != out.shape
-            or not (x.dtype == gate.dtype == out.dtype)):
+    if (gate is None) != (act is None):
+        raise KernelError("gate_mul: a gate and its activation come together")
+    if (per <= 0 or x.shape[1] % per or x.shape != out.shape or x.dtype != out.dtype
+            or (gate is not None and (tuple(gate.shape) != (x.shape[0], x.shape[1] // per) or gate.dtype != x.dtype))):
         raise KernelError("gate_mul: x and out must agree in shape, the gate has a column per group, one dtype")
     lib = _lib("rope_norm")
-    rc = lib.mi_gate_mul(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), x.shape[0],
+    rc = lib.mi_gate_mul(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+                         out.stride(0), x.shape[0],
                          x.shape[1], _ACT[act], float(scale), int(per), _code(x.dtype), _stream())
     _finish(lib, rc, "gate_mul")
 
@@ -1403,14 +1414,19 @@ GLA_CHUNK = 128      # tokens per chunk of the chunked walk of gated linear atte
 
 def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor | None, z_bias: torch.Tensor | None,
              tau: float, q_scale: float, heads: int, dk: int, dv: int, state: torch.Tensor, ctx,
-             head_decay: torch.Tensor | None = None) -> torch.Tensor:
+             head_decay: torch.Tensor | None = None, tok_gates: torch.Tensor | None = None,
+             extra_col: bool = False) -> torch.Tensor:
     """Gated linear attention over each request's portion, from and into its state row
     ``[heads, dk, dv]``: ``S = diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)`` with
     ``alpha = sigmoid(z + z_bias)^(1 / tau)``.  q, k, v: column ranges of one packed projection;
     ``z`` fp32 ``[M, heads * dk]``.  With ``head_decay`` (fp32 ``[heads]``) every head has one fixed
     decay in the place of ``alpha`` and ``z`` is not read (linear attention with a fixed decay, or
-    retention).  Returns fp32 ``o [M, heads * dv]``."""
-    _cuda(q, k, v, z, z_bias, state, head_decay)
+    retention).  With ``tok_gates`` (fp32 ``[M, heads, 3]``) the decay, the same for all key channels, and a
+    factor on ``k`` come per token and head from its first two numbers.  With ``extra_col`` a head of the
+    state and of ``o`` has one more value column, whose values are all ones: the state row is
+    ``[heads, dk, dv + 1]`` and ``o [M, heads * (dv + 1)]``, the last column of a head being ``sum(k) . q``.
+    Returns fp32 ``o [M, heads * dv]``."""
+    _cuda(q, k, v, z, z_bias, state, head_decay, tok_gates)
     for t in (q, k, v) + ((z,) if z is not None else ()):
         _cols(t, "gla")
     M = q.shape[0]
@@ -1420,16 +1436,20 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor 
         raise KernelError("gla: q and k have the values' dtype, or are fp32 beside bfloat16 values")
     if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv:
         raise KernelError("gla: q, k must be [M, heads * dk] and v [M, heads * dv]")
-    if head_decay is None and z is None:
-        raise KernelError("gla: needs z (a decay per channel) or head_decay (one per head)")
+    if head_decay is None and z is None and tok_gates is None:
+        raise KernelError("gla: needs z (a decay per channel), head_decay (one per head) or tok_gates (per token and head)")
+    if tok_gates is not None and (tok_gates.dtype != torch.float32 or tok_gates.shape != (M, heads, 3)
+                                  or not tok_gates.is_contiguous()):
+        raise KernelError("gla: tok_gates must be contiguous fp32 [M, heads, 3]")
+    dvx = dv + (1 if extra_col else 0)
     if z is not None and (z.dtype != torch.float32 or z.shape != (M, heads * dk)):
         raise KernelError("gla: z must be fp32 [M, heads * dk]")
     _f32vec(head_decay, heads, "gla")
     _f32vec(z_bias, heads * dk, "gla")
     stride = _state_rows(state, "gla")
-    if stride < heads * dk * dv:
+    if stride < heads * dk * dvx:
         raise KernelError("gla: state row too short")
-    o = torch.empty((M, heads * dv), dtype=torch.float32, device=q.device)
+    o = torch.empty((M, heads * dvx), dtype=torch.float32, device=q.device)
     lib = _lib("recurrent")
     longest = _max_q_len(ctx)
     n_chunks, scratch = 1, None
@@ -1438,15 +1458,16 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor 
         # sums do not depend on where a portion starts)
         global launch_count
         n_chunks = -(-longest // GLA_CHUNK)
-        scratch = torch.empty(lib.mi_gla_chunked_scratch(ctx.n_requests, n_chunks, heads, dk, dv), dtype=torch.float32,
+        scratch = torch.empty(lib.mi_gla_chunked_scratch(ctx.n_requests, n_chunks, heads, dk, dvx), dtype=torch.float32,
                               device=q.device)
         launch_count += 1
     rc = lib.mi_gla_scan(_ptr(q), _ptr(k), q.stride(0), _code(q.dtype), _ptr(v), v.stride(0), _ptr(z),
                          z.stride(0) if z is not None else 0,
                          _ptr(z_bias), 1.0 / float(tau),
                          float(q_scale), _ptr(state), stride, _ptr(ctx.q_start), _ptr(ctx.q_len),
-                         _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dv, _ptr(scratch),
-                         n_chunks, GLA_CHUNK, _ptr(head_decay), _code(v.dtype), _stream())
+                         _ptr(ctx.state_slot), _ptr(o), o.stride(0), ctx.n_requests, heads, dk, dvx, _ptr(scratch),
+                         n_chunks, GLA_CHUNK, _ptr(head_decay), _ptr(tok_gates), 1 if extra_col else 0,
+                         _code(v.dtype), _stream())
     _finish(lib, rc, "gla")
     return o
 
@@ -1498,49 +1519,100 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
 
 
 def headnorm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, heads: int,
-                  dv: int, eps: float, act: str | None, scale: float = 1.0) -> None:
+                  dv: int, eps: float, act: str | None, scale: float = 1.0, *, tok_gates: torch.Tensor | None = None,
+                  den_eps: float = 0.0) -> None:
     """``out = o / sqrt(mean_head(o^2) + eps) * weight * act(gate) * scale`` per head of ``dv``
-    (``o`` fp32 ``[M, heads * dv]``, ``weight`` fp32 ``[dv]``, ``gate`` and ``out`` in the compute dtype)."""
-    _cuda(o, weight, gate, out)
+    (``o`` fp32 ``[M, heads * dv]``, ``weight`` fp32 ``[dv]``, shared by the heads, or ``[heads * dv]``, ``gate``
+    and ``out`` in the compute dtype).  With ``tok_gates`` (fp32 ``[M, heads, 3]``) a head of ``o`` has
+    ``dv + 1`` columns, the last one a normaliser ``n``, and the head is divided by
+    ``max(|n|, exp(-m)) + den_eps`` first, ``m`` the third number of the token's and head's gates."""
+    _cuda(o, weight, gate, out, tok_gates)
     _cols(o, "headnorm_gate")
     _cols(out, "headnorm_gate")
-    if o.dtype != torch.float32 or o.shape[1] != heads * dv or out.shape != o.shape:
+    dvx = dv + (1 if tok_gates is not None else 0)
+    if o.dtype != torch.float32 or o.shape[1] != heads * dvx or out.shape != (o.shape[0], heads * dv):
         raise KernelError("headnorm_gate: o must be fp32 [M, heads * dv] and out shaped like it")
-    _f32vec(weight, dv, "headnorm_gate")
+    if tok_gates is not None and (tok_gates.dtype != torch.float32 or tok_gates.shape != (o.shape[0], heads, 3)
+                                  or not tok_gates.is_contiguous()):
+        raise KernelError("headnorm_gate: tok_gates must be contiguous fp32 [M, heads, 3]")
+    per_head = weight.numel() == heads * dv and heads > 1
+    _f32vec(weight, heads * dv if per_head else dv, "headnorm_gate")
     if gate is not None:
         _cols(gate, "headnorm_gate")
-        if gate.shape != o.shape or gate.dtype != out.dtype:
+        if gate.shape != out.shape or gate.dtype != out.dtype:
             raise KernelError("headnorm_gate: the gate must match out")
     lib = _lib("recurrent")
     rc = lib.mi_headnorm_gate(_ptr(o), o.stride(0), _ptr(weight), _ptr(gate), gate.stride(0) if gate is not None else 0,
                               _ptr(out), out.stride(0), o.shape[0], heads, dv, float(eps),
-                              _ACT[act if gate is not None else None], float(scale), _code(out.dtype), _stream())
+                              _ACT[act if gate is not None else None], float(scale), dv if per_head else 0,
+                              _ptr(tok_gates), float(den_eps), _code(out.dtype), _stream())
     _finish(lib, rc, "headnorm_gate")
+
+
+def mlstm_gates(z: torch.Tensor, bias_i: torch.Tensor | None, bias_f: torch.Tensor | None, cap: float, heads: int,
+                state: torch.Tensor, m_offset: int, ctx) -> torch.Tensor:
+    """The scalar gates of a matrix memory with a running maximum ``m`` (per request and head at
+    ``m_offset`` of its state row, updated): from the pre-activations ``z`` (fp32 ``[M, 2 heads]``: input
+    gates, then forget gates), ``i = cap tanh((z_i + b_i) / cap)``, ``f = logsigmoid(cap tanh((z_f + b_f) /
+    cap))``, ``m' = max(f + m, i)`` token by token.  Returns fp32 ``[M, heads, 3]``: the state's decay
+    ``exp(f + m - m')``, the input's factor ``exp(i - m')``, and ``m'``."""
+    _cuda(z, bias_i, bias_f, state)
+    _cols(z, "mlstm")
+    M = z.shape[0]
+    if z.dtype != torch.float32 or z.shape[1] != 2 * heads:
+        raise KernelError("mlstm: the gates' pre-activations must be fp32 [M, 2 heads]")
+    _f32vec(bias_i, heads, "mlstm")
+    _f32vec(bias_f, heads, "mlstm")
+    stride = _state_rows(state, "mlstm")
+    gates = torch.empty((M, heads, 3), dtype=torch.float32, device=z.device)
+    lib = _lib("recurrent")
+    rc = lib.mi_mlstm_gates(_ptr(z), _ptr(z[:, heads:]), z.stride(0), _ptr(bias_i), _ptr(bias_f), float(cap),
+                            _ptr(state), stride, int(m_offset), _ptr(ctx.q_start), _ptr(ctx.q_len),
+                            _ptr(ctx.state_slot), _ptr(gates), ctx.n_requests, heads, _stream())
+    _finish(lib, rc, "mlstm")
+    return gates
 
 
 # --------------------------------------------------------------------------------------- routed experts
 
 
+ROUTE_MODES = {"chosen": 0, "all": 1, "sigmoid": 2}
+
+
 def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, all_scores: bool = False, groups: int = 0,
-              keep_groups: int = 0, scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor]:
+              keep_groups: int = 0, scale: float = 1.0, scores: str | None = None,
+              correction: torch.Tensor | None = None, group_top2: bool = False, experts: int | None = None,
+              return_logits: bool = False):
     """fp32 router logits ``x router^T``; per token the ``top`` experts with the largest logits
     (int32 ``[M, top]``, largest first) and their weights (fp32): the softmax over those logits alone,
     or, with ``all_scores``, their scores under the softmax over all experts divided by the sum of
     these (+ 1e-20), times ``scale``.  ``groups`` > 1: the experts form that many equal groups of
-    neighbours, a group counts as its best expert, and only the ``keep_groups`` best groups give experts."""
-    _cuda(x, router)
+    neighbours, a group counts as its best expert, and only the ``keep_groups`` best groups give experts.
+    ``scores`` names the way outright: ``"chosen"``, ``"all"`` or ``"sigmoid"`` (scores are the logits'
+    sigmoids; the choice adds ``correction`` (fp32 ``[experts]``) per expert; the weights are the chosen
+    scores times ``scale``, not renormalised).  ``group_top2``: a group counts as the sum of its two best
+    choice scores.  ``experts``: only the router's first ``experts`` rows are experts; the other rows ride
+    along in the product and ``return_logits`` hands all logits back as a third result."""
+    _cuda(x, router, correction)
     _cols(x, "moe")
     if router.dim() != 2 or router.shape[1] != x.shape[1] or router.dtype != x.dtype or not router.is_contiguous():
         raise KernelError("moe: the router must be a contiguous [experts, H] matrix in x's dtype")
     M, H = x.shape
-    E = router.shape[0]
+    E = router.shape[0] if experts is None else int(experts)
+    if not 0 < E <= router.shape[0]:
+        raise KernelError(f"moe: {E} experts of a router with {router.shape[0]} rows")
+    mode = ROUTE_MODES[scores] if scores is not None else (1 if all_scores else 0)
+    _f32vec(correction, E, "moe (correction)")
     logits = linear(x, router, out_dtype=torch.float32)      # exact products, fp32 sums, for either dtype
     ids = torch.empty((M, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((M, top), dtype=torch.float32, device=x.device)
     lib = _lib("moe")
     rc = lib.mi_moe_select(_ptr(logits), logits.stride(0), _ptr(ids), _ptr(weights), M, E, int(top),
-                           1 if all_scores else 0, int(groups), int(keep_groups), float(scale), _stream())
+                           mode, int(groups), int(keep_groups), float(scale), _ptr(correction),
+                           1 if group_top2 else 0, _stream())
     _finish(lib, rc, "moe_select")
+    if return_logits:
+        return ids, weights, logits
     return ids, weights
 
 
@@ -1550,12 +1622,13 @@ USE_GROUPED_MM = os.environ.get("MINI_INFER_GROUPED_MM", "1") != "0"
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, limit: float, alpha: float, shared: torch.Tensor | None = None,
-                up_offset: float = 1.0) -> torch.Tensor:
+                up_offset: float = 1.0, shared_gate: torch.Tensor | None = None) -> torch.Tensor:
     """``out[t] = sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) (+ shared[t])`` with
     ``expert(x) = W_down glu(W_gate x, W_up x)``, ``glu(g, u) = g' sigmoid(alpha g') (u' + up_offset)``,
     ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` (an infinite ``limit`` with ``alpha`` 1 and
     ``up_offset`` 0 is the plain ``silu(g) * u``).  Weights are stacked per expert:
     ``w_gate_up [E, 2 ff, H]`` (an expert's gate rows, then its up rows), ``w_down [E, H, ff]``.
+    ``shared_gate`` (fp32, one number per token, any row stride): its sigmoid multiplies ``shared[t]``.
     Entries are sorted by expert on the device; nothing is read back.  Three routes: a step that
     brings an expert only a few rows streams the weights (bfloat16); large bfloat16 steps gather
     each expert's rows and use the library's grouped product (as the dense layers use the library's
@@ -1610,9 +1683,12 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
                              _stream())
         _finish(lib, rc, "moe_down")
     out = torch.empty((M, H), dtype=x.dtype, device=dev)
+    if shared_gate is not None and (shared is None or shared_gate.dtype != torch.float32 or shared_gate.shape[0] != M
+                                    or shared_gate.dim() > 2 or (shared_gate.dim() == 2 and shared_gate.shape[1] != 1)):
+        raise KernelError("moe: the shared expert's gate must be fp32, one number per token, beside a shared expert")
     rc = lib.mi_moe_combine(_ptr(y), _code(y.dtype), _ptr(inv), _ptr(weights), _ptr(shared),
-                            shared.stride(0) if shared is not None else 0, _ptr(out), M, H, top, _code(x.dtype),
-                            _stream())
+                            shared.stride(0) if shared is not None else 0, _ptr(out), M, H, top, _ptr(shared_gate),
+                            shared_gate.stride(0) if shared_gate is not None else 0, _code(x.dtype), _stream())
     _finish(lib, rc, "moe_combine")
     return out
 
@@ -1754,6 +1830,60 @@ def glu_mul_pairs(gate_up: torch.Tensor, act: str, out: torch.Tensor | None = No
     return out
 
 
+def scaled_norm_add(stream: torch.Tensor, branch: torch.Tensor | None, gain: torch.Tensor | None, eps: float,
+                    mult: float, dtype: torch.dtype, copy: bool = True) -> torch.Tensor | None:
+    """A branch whose norm stands behind it: ``stream += mult * y * rsqrt(mean(y^2) + eps) * gain`` in place
+    (``stream`` fp32 ``[M, H]``, ``y`` the branch's rows in ``dtype``, ``gain`` fp32 ``[H]``).  Returns the
+    updated stream's copy in ``dtype`` (what the next branch's products read), or, for float32, the
+    stream itself.  Without a branch only the copy is made."""
+    _cuda(stream, branch, gain)
+    if stream.dtype != torch.float32 or stream.dim() != 2 or not stream.is_contiguous():
+        raise KernelError("norm_add: the stream must be contiguous fp32 [M, H]")
+    M, H = stream.shape
+    if branch is not None:
+        _cols(branch, "norm_add")
+        if branch.shape != (M, H) or branch.dtype != dtype:
+            raise KernelError("norm_add: the branch must be [M, H] in the compute dtype")
+        _f32vec(gain, H, "norm_add")
+    out = None
+    if copy and dtype != torch.float32:
+        out = torch.empty((M, H), dtype=dtype, device=stream.device)
+    if branch is None and out is None:
+        return stream
+    lib = _lib("stream")
+    rc = lib.mi_scaled_norm_add(_ptr(stream), _ptr(branch), branch.stride(0) if branch is not None else 0, _ptr(gain),
+                                float(eps), float(mult), _ptr(out), M, H, _code(dtype), _stream())
+    _finish(lib, rc, "norm_add")
+    return stream if dtype == torch.float32 else out
+
+
+def token_gate(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int) -> torch.Tensor:
+    """``gelu_tanh(z[t, c]) * table[ids[t], col0 + c]`` for ``z [M, n]`` (fp32 or the table's dtype), in the
+    table's dtype."""
+    _cuda(z, table, ids)
+    _cols(z, "token_gate")
+    if table.dim() != 2 or not table.is_contiguous() or ids.dtype != torch.int32 or ids.shape != (z.shape[0],):
+        raise KernelError("token_gate: a contiguous table [V, columns] and int32 ids [M]")
+    M, n = z.shape
+    out = torch.empty((M, n), dtype=table.dtype, device=z.device)
+    lib = _lib("stream")
+    rc = lib.mi_token_gate(_ptr(z), z.stride(0), _code(z.dtype), _ptr(table), table.stride(0), _ptr(ids),
+                           table.shape[0], int(col0), _ptr(out), M, n, _code(table.dtype), _stream())
+    _finish(lib, rc, "token_gate")
+    return out
+
+
+def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
+    """``x *= s`` in place (contiguous fp32)."""
+    _cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale: a contiguous fp32 tensor")
+    lib = _lib("stream")
+    rc = lib.mi_scale_f32(_ptr(x), x.numel(), float(s), _stream())
+    _finish(lib, rc, "scale")
+    return x
+
+
 # --------------------------------------------------------------------------------------- between projection and attention
 
 
@@ -1805,7 +1935,8 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
                        freq: torch.Tensor | None = None, q_scale: float = 1.0, k_scale: float = 1.0,
                        v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
                        slots: torch.Tensor | None = None, kcache: torch.Tensor | None = None,
-                       vcache: torch.Tensor | None = None, qk_out: torch.Tensor | None = None) -> None:
+                       vcache: torch.Tensor | None = None, qk_out: torch.Tensor | None = None,
+                       bias: torch.Tensor | None = None) -> None:
     """In the packed projection ``[M, stride]`` (q at columns ``q_off``, ``nq`` heads of ``d``; k at
     ``k_off``, ``nkv`` heads of ``d``; v at ``v_off``, ``nkv`` heads of ``dv``, or ``v_off`` None: no values
     here): q and k get an RMS norm over the head with the gain shared by the heads (fp32 ``[d]``; None:
@@ -1814,8 +1945,9 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
     written back.  With ``v_other`` (``[M, nkv * dv]``) and ``blend`` (fp32, one element) the values
     become ``(1 - blend) v + blend v_other`` and are written back too.  With caches, k and v are stored
     at ``slots``.  With ``qk_out`` (fp32 ``[M, (nq + nkv) * d]``, queries first) the finished q and k go there
-    unrounded and their packed columns stay as they were: for a recurrence that takes them in fp32."""
-    _cuda(packed, q_gain, k_gain, positions, freq, v_other, blend, slots, kcache, vcache, qk_out)
+    unrounded and their packed columns stay as they were: for a recurrence that takes them in fp32.
+    ``bias`` (fp32, one number per packed column up to the last of q, k and v) is added to q, k and v first."""
+    _cuda(packed, q_gain, k_gain, positions, freq, v_other, blend, slots, kcache, vcache, qk_out, bias)
     _cols(packed, "qk_prepare")
     M, width = packed.shape
     has_v = v_off is not None
@@ -1848,13 +1980,17 @@ def qk_norm_rope_store(packed: torch.Tensor, q_off: int, k_off: int, v_off: int 
     if qk_out is not None and (qk_out.dtype != torch.float32 or qk_out.shape != (M, (nq + nkv) * d)
                                or qk_out.stride(1) != 1):
         raise KernelError("qk_prepare: qk_out must be fp32 [M, (nq + nkv) * d]")
+    if bias is not None:
+        need = max(q_off + nq * d, k_off + nkv * d, (v_off + nkv * dv) if has_v else 0)
+        if bias.dtype != torch.float32 or bias.dim() != 1 or bias.shape[0] < need or not bias.is_contiguous():
+            raise KernelError(f"qk_prepare: the bias must be fp32 with at least {need} numbers")
     lib = _lib("qk_prepare")
     rc = lib.mi_qk_norm_rope_store(_ptr(packed), packed.stride(0), q_off, k_off, v_off if has_v else -1, M, nq, nkv, d,
                                    dv, _ptr(q_gain), _ptr(k_gain), float(eps), int(rot), _ptr(positions), _ptr(freq),
                                    float(q_scale), float(k_scale), _ptr(v_other),
                                    v_other.stride(0) if v_other is not None else 0, _ptr(blend), _ptr(slots),
                                    _ptr(kcache), _ptr(vcache if has_v else None), page_size, 1 if writes else 0,
-                                   _ptr(qk_out), qk_out.stride(0) if qk_out is not None else 0,
+                                   _ptr(qk_out), qk_out.stride(0) if qk_out is not None else 0, _ptr(bias),
                                    _code(packed.dtype), _stream())
     _finish(lib, rc, "qk_prepare")
 

@@ -23,7 +23,8 @@
 //                           the angle is computed and reduced to [-pi, pi] in double precision, its sine
 //                           and cosine in fp32.
 //   mi_qk_norm_rope_store   queries and keys get an RMS norm over the head with one gain shared by the heads
-//                           (optional), then the rotation of the half layout on their first `rot` dimensions
+//                           (optional; before it an fp32 bias per packed column may be added to q, k and v),
+//                           then the rotation of the half layout on their first `rot` dimensions
 //                           (angles as above), then a factor each (q_scale, k_scale); both are written back
 //                           in place and k goes to its cache page.  The values (optional: v_off < 0 means the
 //                           mixer has none here) may be blended with another layer's values of the same
@@ -237,7 +238,8 @@ qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
                           float k_scale, const T* __restrict__ v_other, int v_other_stride,
                           const float* __restrict__ lam_ptr, const int* __restrict__ slots, T* __restrict__ kcache,
                           T* __restrict__ vcache, int page_size, int writes, float* __restrict__ qk_out,
-                          int qk_out_stride) {
+                          int qk_out_stride, const float* __restrict__ bias) {
+  // bias [stride]: added (fp32) to the q, k and v columns before anything else, by packed column.
   // qk_out [M, (nq + nkv) * d] fp32: the finished queries and keys go there unrounded (for a recurrence
   // that reads them in fp32) and the packed rows keep what the projection left.
   mi_pdl_enter();
@@ -276,6 +278,10 @@ qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
       const T* other = v_other ? v_other + (size_t)t * v_other_stride + kvh * dv : nullptr;
       for (int k = lane; k < dv; k += 32) {
         T y = src[k];
+        if (bias) {
+          y = mi_from_float<T>(mi_to_float(y) + bias[v_off + kvh * dv + k]);
+          if (!other) src[k] = y;
+        }
         if (other) {
           y = mi_from_float<T>((1.f - lam) * mi_to_float(y) + lam * mi_to_float(other[k]));
           src[k] = y;
@@ -290,8 +296,9 @@ qk_norm_rope_store_kernel(T* __restrict__ packed, int stride, int q_off, int k_o
     const float* gain = is_q ? q_gain : k_gain;
     const float post = is_q ? q_scale : k_scale;
     float ss = 0.f;
+    const float* xb = bias ? bias + (is_q ? q_off : k_off) + hh * d : nullptr;
     for (int k = lane; k < d; k += 32) {
-      const float v = mi_to_float(x[k]);
+      const float v = mi_to_float(x[k]) + (xb ? xb[k] : 0.f);
       mine[k] = v;
       ss += v * v;
     }
@@ -324,7 +331,7 @@ extern "C" int mi_qk_norm_rope_store(void* packed, int stride, int q_off, int k_
                                      const int* positions, const double* freq, float q_scale, float k_scale,
                                      const void* v_other, int v_other_stride, const float* lam, const int* slots,
                                      void* kcache, void* vcache, int page_size, int writes, float* qk_out,
-                                     int qk_out_stride, int dtype, cudaStream_t stream) {
+                                     int qk_out_stride, const float* bias, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (qk_out && qk_out_stride < (nq + nkv) * d) MI_REFUSE("qk_prepare: fp32 rows of %d for %d heads of %d", qk_out_stride, nq + nkv, d);
   if (d <= 0 || d > ROPE_MAX_D || dv < 0) MI_REFUSE("qk_prepare: head size %d must lie in [1, %d]", d, ROPE_MAX_D);
@@ -339,7 +346,7 @@ extern "C" int mi_qk_norm_rope_store(void* packed, int stride, int q_off, int k_
 #define MI_GO(T)                                                                                                       \
   MI_LAUNCH((qk_norm_rope_store_kernel<T>), grid, 128, smem, stream, (T*)packed, stride, q_off, k_off, v_off, nq, nkv, \
             d, dv, q_gain, k_gain, eps, rot, positions, freq, q_scale, k_scale, (const T*)v_other, v_other_stride,    \
-            lam, slots, (T*)kcache, (T*)vcache, page_size, writes, qk_out, qk_out_stride)
+            lam, slots, (T*)kcache, (T*)vcache, page_size, writes, qk_out, qk_out_stride, bias)
   if (dtype == MI_DTYPE_F32) MI_GO(float);
   else if (dtype == MI_DTYPE_BF16) MI_GO(bf16);
   else MI_REFUSE("qk_prepare: unknown dtype %d", dtype);

@@ -15,6 +15,12 @@
 //                      and, for the convolution in front of it, the new last taps-1 inputs.
 //   mi_gla_scan        gated linear attention, per head: S = diag(alpha) S + k v^T, o = S^T (q * qscale),
 //                      alpha = sigmoid(z + bz)^(1/tau), or one fixed decay per head (head_decay).
+//                      Optionally the decay and a factor on k come per token and head from a table
+//                      (tok_gates), and one more value column of ones rides along (extra_col): the
+//                      state then holds sum(k) beside sum(k v^T), a normaliser.
+//   mi_mlstm_gates     the scalar gates of a matrix memory with a running maximum, per head and token:
+//                        i = cap tanh((zi + bi) / cap), f = logsigmoid(cap tanh((zf + bf) / cap)),
+//                        m' = max(f + m, i);  gates = (exp(f + m - m'), exp(i - m'), m');  m <- m'
 //   mi_delta_scan      the gated delta rule with a decay per key channel, per head:
 //                        S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                      with q and k made unit vectors per head first (q also times q_scale),
@@ -315,8 +321,12 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q
                                 const int* __restrict__ q_start, const int* __restrict__ q_len,
                                 const int* __restrict__ state_slot, float* __restrict__ o, int o_stride,
                                 int heads, int dk, int dv, int pass, int chunk_len, int n_chunks,
-                                float* __restrict__ scratch, const float* __restrict__ head_decay) {
+                                float* __restrict__ scratch, const float* __restrict__ head_decay,
+                                const float* __restrict__ tok_gates, int extra_col) {
   // head_decay [heads]: one fixed decay per head in the place of alpha (z is then not read).
+  // tok_gates [M, heads, 3]: per token and head the decay (all key channels alike) and a factor on k
+  // (z and head_decay are then not read).  extra_col: the head has dv + 1 value columns, the last one
+  // all ones, in the state and in o alike (dv below counts it; v has one column less).
   // q and k may be fp32 rows of their own (what a rotation left in fp32) beside bfloat16 values.
   // pass 0: the whole portion, from and into the state.  Long portions run as chunks side by side:
   // pass 1 folds every chunk into (A, B) with S_end = diag(A) S_begin + B (and saves the state the
@@ -334,6 +344,7 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q
   const int tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx, nthreads = KP * 32;
   const int head = blockIdx.y, req = blockIdx.z / n_chunks, chunk = blockIdx.z - req * n_chunks;
   const int j = blockIdx.x * 32 + tx;   // value column
+  const int dv_in = dv - extra_col;     // columns that v brings
   const int len_all = q_len[req];
   const int c0 = pass ? chunk * chunk_len : 0;
   if (c0 >= len_all) return;
@@ -379,7 +390,13 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q
         const size_t m = (size_t)(row0 + t0 + l);
         pq[i] = mi_to_float(q[m * qk_stride + head * dk + kk]);
         pk[i] = mi_to_float(k[m * qk_stride + head * dk + kk]);
-        pz[i] = head_decay ? 0.f : z[m * z_stride + head * dk + kk];
+        if (tok_gates) {
+          const float* tg = tok_gates + (m * heads + head) * 3;
+          pz[i] = tg[0];
+          pk[i] *= tg[1];
+        } else {
+          pz[i] = head_decay ? 0.f : z[m * z_stride + head * dk + kk];
+        }
       }
     }
 #pragma unroll
@@ -387,7 +404,8 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q
       const int idx = tid + i * nthreads;
       if (idx < n * 32) {
         const int l = idx >> 5, jj = blockIdx.x * 32 + (idx & 31);
-        pv[i] = jj < dv ? mi_to_float(v[(size_t)(row0 + t0 + l) * stride + head * dv + jj]) : 0.f;
+        pv[i] = jj < dv_in ? mi_to_float(v[(size_t)(row0 + t0 + l) * stride + head * dv_in + jj])
+                           : (jj < dv ? 1.f : 0.f);
       }
     }
   };
@@ -402,8 +420,8 @@ __global__ void __launch_bounds__(MAXT) gla_scan_kernel(const TQ* __restrict__ q
         const int kk = idx % dk;
         qs[idx] = pq[i] * q_scale;
         ks[idx] = pk[i];
-        const float zz = pz[i] + (z_bias ? z_bias[head * dk + kk] : 0.f);
-        as[idx] = head_decay ? head_decay[head]
+        const float zz = pz[i] + ((z_bias && !tok_gates) ? z_bias[head * dk + kk] : 0.f);
+        as[idx] = tok_gates ? pz[i] : head_decay ? head_decay[head]
                              : expf(-mi_softplus(-zz) * inv_tau);     // sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau)
       }
     }
@@ -459,9 +477,13 @@ extern "C" int mi_gla_scan(const void* q, const void* k, int qk_stride, int qk_d
                            const float* z_bias, float inv_tau, float q_scale, float* state, long long state_stride,
                            const int* q_start, const int* q_len, const int* state_slot, float* o, int o_stride,
                            int n_requests, int heads, int dk, int dv, float* scratch, int n_chunks, int chunk_len,
-                           const float* head_decay, int dtype, cudaStream_t stream) {
+                           const float* head_decay, const float* tok_gates, int extra_col, int dtype,
+                           cudaStream_t stream) {
+  // dv counts the value columns of the state and of o; with extra_col v brings one less
   if (n_requests <= 0) return 0;
-  if (!z && !head_decay) MI_REFUSE("gla: neither decays per channel nor decays per head");
+  if (!z && !head_decay && !tok_gates) MI_REFUSE("gla: neither decays per channel nor per head nor per token");
+  if (extra_col != 0 && extra_col != 1) MI_REFUSE("gla: one extra column or none");
+  if (dv - extra_col <= 0) MI_REFUSE("gla: no value columns");
   if (n_chunks < 1 || (n_chunks > 1 && (!scratch || chunk_len <= 0))) MI_REFUSE("gla: chunks need scratch memory");
   if ((long long)n_requests * n_chunks > 65535) MI_REFUSE("gla: too many chunks for one launch");
   if (dk <= 0 || dk > 256 || dv <= 0) MI_REFUSE("gla: key size %d must lie in [1, 256], value size %d above 0", dk, dv);
@@ -479,13 +501,86 @@ extern "C" int mi_gla_scan(const void* q, const void* k, int qk_stride, int qk_d
     for (int pass = n_chunks > 1 ? 1 : 0; pass <= (n_chunks > 1 ? 2 : 0); ++pass)                         \
       MI_LAUNCH(kern, grid, block, smem, stream, (const TQ*)q, (const TQ*)k, qk_stride, (const T*)v, stride, z, z_stride, \
                 z_bias, inv_tau, q_scale, state, state_stride, q_start, q_len, state_slot, o, o_stride, heads, \
-                dk, dv, pass, chunk_len, n_chunks, scratch, head_decay);                                   \
+                dk, dv, pass, chunk_len, n_chunks, scratch, head_decay, tok_gates, extra_col);              \
   } while (0)
   if (dtype == MI_DTYPE_F32 && qk_dtype == MI_DTYPE_F32) MI_GO(float, float);
   else if (dtype == MI_DTYPE_BF16 && qk_dtype == MI_DTYPE_BF16) MI_GO(bf16, bf16);
   else if (dtype == MI_DTYPE_BF16 && qk_dtype == MI_DTYPE_F32) MI_GO(float, bf16);
   else MI_REFUSE("gla: dtypes %d (q, k) and %d (v) are not taken together", qk_dtype, dtype);
 #undef MI_GO
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------------------------------
+// scalar gates of a matrix memory with a running maximum.  One warp per (request, head) walks the
+// portion 32 tokens at a time: the lanes compute the capped log gates of their tokens, lane 0 walks
+// m' = max(f + m, i) through them in the order of the positions (one addition and one maximum per
+// token, whatever the cutting), the lanes turn (m, m') into the decay and the input factor.
+// state row of a request: m [heads] at m_offset.
+// ------------------------------------------------------------------------------------------
+#define MLSTM_WARPS 4
+__global__ void __launch_bounds__(32 * MLSTM_WARPS)
+mlstm_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, int z_stride,
+                   const float* __restrict__ bi, const float* __restrict__ bf_, float cap,
+                   float* __restrict__ state, long long state_stride, long long m_offset,
+                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                   const int* __restrict__ state_slot, float* __restrict__ gates, int n_requests, int heads) {
+  mi_pdl_enter();
+  __shared__ float sh_i[MLSTM_WARPS][32], sh_f[MLSTM_WARPS][32], sh_m[MLSTM_WARPS][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int unit = blockIdx.x * MLSTM_WARPS + warp;
+  if (unit >= n_requests * heads) return;
+  const int req = unit / heads, head = unit - req * heads;
+  const int len = q_len[req], row0 = q_start[req];
+  float* mp = state + (size_t)state_slot[req] * state_stride + m_offset + head;
+  const float inv_cap = 1.f / cap;
+  const float b_i = bi ? bi[head] : 0.f, b_f = bf_ ? bf_[head] : 0.f;
+  float m = *mp;
+  for (int t0 = 0; t0 < len; t0 += 32) {
+    const int n = min(32, len - t0);
+    float gi = 0.f, gf = 0.f;
+    if (lane < n) {
+      const size_t r = (size_t)(row0 + t0 + lane);
+      gi = cap * tanhf((zi[r * z_stride + head] + b_i) * inv_cap);
+      const float a = cap * tanhf((zf[r * z_stride + head] + b_f) * inv_cap);
+      gf = -mi_softplus(-a);                  // logsigmoid
+    }
+    sh_i[warp][lane] = gi;
+    sh_f[warp][lane] = gf;
+    __syncwarp();
+    if (lane == 0) {
+      float run = m;
+      sh_m[warp][0] = run;
+#pragma unroll 8
+      for (int l = 0; l < n; ++l) {
+        run = fmaxf(sh_f[warp][l] + run, sh_i[warp][l]);
+        sh_m[warp][l + 1] = run;
+      }
+    }
+    __syncwarp();
+    if (lane < n) {
+      const float before = sh_m[warp][lane], after = sh_m[warp][lane + 1];
+      float* gp = gates + ((size_t)(row0 + t0 + lane) * heads + head) * 3;
+      gp[0] = expf(gf + before - after);
+      gp[1] = expf(gi - after);
+      gp[2] = after;
+    }
+    m = sh_m[warp][n];
+    __syncwarp();
+  }
+  if (lane == 0 && len > 0) *mp = m;
+}
+
+extern "C" int mi_mlstm_gates(const float* zi, const float* zf, int z_stride, const float* bi, const float* bf_,
+                              float cap, float* state, long long state_stride, long long m_offset,
+                              const int* q_start, const int* q_len, const int* state_slot, float* gates,
+                              int n_requests, int heads, cudaStream_t stream) {
+  if (n_requests <= 0 || heads <= 0) return 0;
+  if (!(cap > 0.f)) MI_REFUSE("mlstm: the gates' cap must be positive, got %g", (double)cap);
+  if (m_offset < 0 || m_offset + heads > state_stride) MI_REFUSE("mlstm: the running maxima lie outside the state row");
+  const int units = n_requests * heads;
+  MI_LAUNCH((mlstm_gates_kernel), (units + MLSTM_WARPS - 1) / MLSTM_WARPS, 32 * MLSTM_WARPS, 0, stream, zi, zf, z_stride,
+            bi, bf_, cap, state, state_stride, m_offset, q_start, q_len, state_slot, gates, n_requests, heads);
   MI_RETURN_LAUNCH_STATUS();
 }
 
@@ -716,22 +811,32 @@ extern "C" int mi_delta_scan(const void* q, const void* k, const void* v, int st
 }
 
 // ------------------------------------------------------------------------------------------
-// per-head RMS norm with a shared gain, times an activated gate.  One warp per (token, head).
+// per-head RMS norm with a gain (shared by the heads: w_head = 0; one per head: w_head = dv), times an
+// activated gate.  One warp per (token, head).  With tok_gates [M, heads, 3] a head of o has dv + 1
+// columns, the last one a normaliser n, and the head is first divided by max(|n|, exp(-m)) + den_eps,
+// m the third number of the token's and head's gates (a matrix memory with a running maximum).
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void headnorm_gate_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ w,
                                      const T* __restrict__ g, int g_stride, T* __restrict__ out, int out_stride,
-                                     int M, int heads, int dv, float eps, int act, float scale) {
+                                     int M, int heads, int dv, float eps, int act, float scale, int w_head,
+                                     const float* __restrict__ tok_gates, float den_eps) {
   mi_pdl_enter();
   const int lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (unit >= (long long)M * heads) return;
   const int t = (int)(unit / heads), h = (int)(unit - (long long)t * heads);
-  const float* src = o + (size_t)t * o_stride + h * dv;
+  const float* src = o + (size_t)t * o_stride + (size_t)h * (dv + (tok_gates ? 1 : 0));
+  float inv_den = 1.f;
+  if (tok_gates) inv_den = 1.f / (fmaxf(fabsf(src[dv]), expf(-tok_gates[((size_t)t * heads + h) * 3 + 2])) + den_eps);
+  w += (size_t)h * w_head;
   float ss = 0.f;
-  for (int c = lane; c < dv; c += 32) ss += src[c] * src[c];
+  for (int c = lane; c < dv; c += 32) {
+    const float v = src[c] * inv_den;
+    ss += v * v;
+  }
   ss = mi_warp_sum(ss);
-  const float mult = 1.f / sqrtf(ss / (float)dv + eps);
+  const float mult = inv_den / sqrtf(ss / (float)dv + eps);
   for (int c = lane; c < dv; c += 32) {
     float a = 1.f;
     if (act) {
@@ -745,7 +850,8 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o, int o_stride, 
 
 extern "C" int mi_headnorm_gate(const float* o, int o_stride, const float* w, const void* g, int g_stride,
                                 void* out, int out_stride, int M, int heads, int dv, float eps, int act,
-                                float scale, int dtype, cudaStream_t stream) {
+                                float scale, int w_head, const float* tok_gates, float den_eps, int dtype,
+                                cudaStream_t stream) {
   if (M <= 0 || heads <= 0) return 0;
   if (act < 0 || act > 2) MI_REFUSE("headnorm_gate: unknown activation %d", act);
   const long long units = (long long)M * heads;
@@ -753,10 +859,10 @@ extern "C" int mi_headnorm_gate(const float* o, int o_stride, const float* w, co
   if (blocks > 0x7fffffffLL) MI_REFUSE("headnorm_gate: too many blocks for one launch");
   if (dtype == MI_DTYPE_F32)
     MI_LAUNCH((headnorm_gate_kernel<float>), (unsigned)blocks, 128, 0, stream, o, o_stride, w, (const float*)g,
-              g_stride, (float*)out, out_stride, M, heads, dv, eps, act, scale);
+              g_stride, (float*)out, out_stride, M, heads, dv, eps, act, scale, w_head, tok_gates, den_eps);
   else if (dtype == MI_DTYPE_BF16)
     MI_LAUNCH((headnorm_gate_kernel<bf16>), (unsigned)blocks, 128, 0, stream, o, o_stride, w, (const bf16*)g,
-              g_stride, (bf16*)out, out_stride, M, heads, dv, eps, act, scale);
+              g_stride, (bf16*)out, out_stride, M, heads, dv, eps, act, scale, w_head, tok_gates, den_eps);
   else
     MI_REFUSE("headnorm_gate: unknown dtype %d", dtype);
   MI_RETURN_LAUNCH_STATUS();

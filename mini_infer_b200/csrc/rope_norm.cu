@@ -120,9 +120,12 @@ __global__ void gate_mul_kernel(const T* __restrict__ x, int x_stride, const T* 
   const size_t n = (size_t)M * C;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(idx / C), c = (int)(idx - (size_t)t * C);
-    const float gv = mi_to_float(g[(size_t)t * g_stride + c / per]);
-    const float sg = 1.f / (1.f + expf(-gv));
-    const float a = act == 2 ? gv * sg : sg;
+    float a = 1.f;                       // act 0: no gate, the factor alone
+    if (act) {
+      const float gv = mi_to_float(g[(size_t)t * g_stride + c / per]);
+      const float sg = 1.f / (1.f + expf(-gv));
+      a = act == 2 ? gv * sg : sg;
+    }
     out[(size_t)t * out_stride + c] = mi_from_float<T>(mi_to_float(x[(size_t)t * x_stride + c]) * a * scale);
   }
 }
@@ -131,7 +134,7 @@ extern "C" int mi_gate_mul(const void* x, int x_stride, const void* g, int g_str
                            int M, int C, int act, float scale, int per, int dtype, cudaStream_t stream) {
   if (M <= 0 || C <= 0) return 0;
   if (per <= 0) MI_REFUSE("gate_mul: %d columns per gate", per);
-  if (act != 1 && act != 2) MI_REFUSE("gate_mul: unknown activation %d", act);
+  if (act < 0 || act > 2 || (act && !g)) MI_REFUSE("gate_mul: unknown activation %d, or no gate for it", act);
   const size_t n = (size_t)M * C;
   const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
   if (dtype == MI_DTYPE_F32)

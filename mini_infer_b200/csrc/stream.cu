@@ -15,6 +15,12 @@
 //                            One block per output row; src = rows[i] when a gather list is given, else i.
 //   mi_glu_mul_pairs         out[m, i] = T(act(gu[m, 2i]) * gu[m, 2i + 1]), act = SiLU (1) or the tanh form
 //                            of GELU (2): the layout of a merged gate/up product whose rows alternate.
+//   mi_scaled_norm_add       a branch whose norm stands behind it: stream[t, :] += mult * y * rsqrt(mean(y^2) + eps)
+//                            * gain with y = float(branch[t, :]), in place (fp32), and copy[t, :] = T(stream[t, :]),
+//                            what the next branch's products read.  Without a branch: the copy alone.
+//   mi_token_gate            out[t, c] = T(gelu_tanh(z[t, c]) * float(table[id_t, col0 + c])): a gate times the
+//                            columns [col0, col0 + n) of a token's row of a table.
+//   mi_scale_f32             x *= s in place (fp32).
 #include "common.cuh"
 
 MI_DEFINE_ERROR_API()
@@ -226,5 +232,98 @@ extern "C" int mi_embedding_rmsnorm(const void* table, const int* ids, const flo
     MI_LAUNCH((embedding_rmsnorm_kernel<bf16>), M, threads, 0, stream, (const bf16*)table, ids, gain, out, H, V, eps);
   else
     MI_REFUSE("embedding: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+
+template <typename T>
+__global__ void scaled_norm_add_kernel(float* __restrict__ stream, const T* __restrict__ branch, int branch_stride,
+                                       const float* __restrict__ gain, float eps, float mult, T* __restrict__ copy,
+                                       int H) {
+  mi_pdl_enter();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  float* sr = stream + (size_t)t * H;
+  T* cp = copy ? copy + (size_t)t * H : nullptr;
+  if (!branch) {
+    for (int k = threadIdx.x; k < H; k += blockDim.x) cp[k] = mi_from_float<T>(sr[k]);
+    return;
+  }
+  const T* y = branch + (size_t)t * branch_stride;
+  float sq = 0.f;
+  for (int k = threadIdx.x; k < H; k += blockDim.x) {
+    const float v = mi_to_float(y[k]);
+    sq += v * v;
+  }
+  const float rstd = 1.f / sqrtf(mi_block_sum(sq, red) / (float)H + eps);
+  for (int k = threadIdx.x; k < H; k += blockDim.x) {
+    const float r = sr[k] + mult * (mi_to_float(y[k]) * rstd * gain[k]);
+    sr[k] = r;
+    if (cp) cp[k] = mi_from_float<T>(r);
+  }
+}
+
+extern "C" int mi_scaled_norm_add(float* stream, const void* branch, int branch_stride, const float* gain, float eps,
+                                  float mult, void* copy, int M, int H, int dtype, cudaStream_t stream_) {
+  if (M <= 0) return 0;
+  if (H <= 0) MI_REFUSE("norm_add: bad width %d", H);
+  if (!stream || (branch && !gain) || (!branch && !copy)) MI_REFUSE("norm_add: a stream and a branch with its gain, or a copy to make");
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  if (dtype == MI_DTYPE_F32)
+    MI_LAUNCH((scaled_norm_add_kernel<float>), M, threads, 0, stream_, stream, (const float*)branch, branch_stride, gain,
+              eps, mult, (float*)copy, H);
+  else if (dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((scaled_norm_add_kernel<bf16>), M, threads, 0, stream_, stream, (const bf16*)branch, branch_stride, gain,
+              eps, mult, (bf16*)copy, H);
+  else
+    MI_REFUSE("norm_add: unknown dtype %d", dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+template <typename TZ, typename T>
+__global__ void token_gate_kernel(const TZ* __restrict__ z, int z_stride, const T* __restrict__ table, int table_stride,
+                                  const int* __restrict__ ids, int V, int col0, T* __restrict__ out, int M, int n) {
+  mi_pdl_enter();
+  const size_t total = (size_t)M * n;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / n), c = (int)(idx - (size_t)t * n);
+    const int id = ids[t];
+    float e = __int_as_float(0x7fc00000);      // the step function validates ids; this keeps a fault visible
+    if ((unsigned)id < (unsigned)V) e = mi_to_float(table[(size_t)id * table_stride + col0 + c]);
+    out[idx] = mi_from_float<T>(glu_act(mi_to_float(z[(size_t)t * z_stride + c]), 2) * e);
+  }
+}
+
+// z_dtype: the gate's pre-activations are fp32 or in the compute dtype
+extern "C" int mi_token_gate(const void* z, int z_stride, int z_dtype, const void* table, int table_stride,
+                             const int* ids, int V, int col0, void* out, int M, int n, int dtype, cudaStream_t stream) {
+  if (M <= 0 || n <= 0) return 0;
+  if (col0 < 0 || col0 + n > table_stride || V <= 0) MI_REFUSE("token_gate: columns %d..%d of a row of %d", col0, col0 + n, table_stride);
+  const size_t total = (size_t)M * n;
+  const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+  if (dtype == MI_DTYPE_F32 && z_dtype == MI_DTYPE_F32)
+    MI_LAUNCH((token_gate_kernel<float, float>), blocks, 256, 0, stream, (const float*)z, z_stride, (const float*)table,
+              table_stride, ids, V, col0, (float*)out, M, n);
+  else if (dtype == MI_DTYPE_BF16 && z_dtype == MI_DTYPE_F32)
+    MI_LAUNCH((token_gate_kernel<float, bf16>), blocks, 256, 0, stream, (const float*)z, z_stride, (const bf16*)table,
+              table_stride, ids, V, col0, (bf16*)out, M, n);
+  else if (dtype == MI_DTYPE_BF16 && z_dtype == MI_DTYPE_BF16)
+    MI_LAUNCH((token_gate_kernel<bf16, bf16>), blocks, 256, 0, stream, (const bf16*)z, z_stride, (const bf16*)table,
+              table_stride, ids, V, col0, (bf16*)out, M, n);
+  else
+    MI_REFUSE("token_gate: unsupported dtypes %d (table) and %d (gate)", dtype, z_dtype);
+  MI_RETURN_LAUNCH_STATUS();
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float s) {
+  mi_pdl_enter();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x)
+    x[idx] *= s;
+}
+
+extern "C" int mi_scale_f32(float* x, long long n, float s, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  MI_LAUNCH((scale_f32_kernel), blocks, 256, 0, stream, x, (size_t)n, s);
   MI_RETURN_LAUNCH_STATUS();
 }

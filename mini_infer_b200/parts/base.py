@@ -282,6 +282,20 @@ class BranchSum(tuple):
         return out
 
 
+class StreamCopy(BranchSum):
+    """What a layer hands on when nothing is left to add: the fp32 stream is up to date, and ``rounded`` is
+    its copy in the compute dtype (for float32 the stream itself), which the next layer's products read.
+    To a part that only knows ``BranchSum`` it is an empty sum."""
+
+    rounded: torch.Tensor | None = None
+
+    @classmethod
+    def of(cls, rounded: torch.Tensor) -> "StreamCopy":
+        c = cls(())
+        c.rounded = rounded
+        return c
+
+
 class Norm(Part):
     # What kind of unfinished norm this class can leave to the products around it (``"rms"``: the
     # product before adds to the stream, multiplies by the gain and leaves sums of squares; the

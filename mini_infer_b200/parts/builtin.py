@@ -26,6 +26,8 @@ from .base import (
     PlanNeeds,
     Position,
     StepContext,
+    StreamCopy,
+    StreamPart,
     StreamSink,
     register_arrangement,
     register_embedding,
@@ -34,6 +36,7 @@ from .base import (
     register_mixer,
     register_norm,
     register_position,
+    register_stream_part,
 )
 
 
@@ -184,6 +187,51 @@ class LayerNorm(Norm):
         return a, b, stream
 
 
+class BranchRMSNorm(Norm):
+    """An RMS norm that stands behind a branch instead of in front of it: the branch reads the stream
+    itself, and the stream takes ``mult * w * y * rsqrt(mean(y^2) + eps)`` of the branch's output ``y``
+    (``add_branch``).  The statistics, the product with the gain and the sum are fp32.
+
+    params: ``hidden_size``, ``eps``, optional ``mult`` (default 1).  tensors: ``weight [hidden_size]``.
+    """
+
+    def param_decls(self):
+        return {"weight": ParamDecl((int(self.param("hidden_size")),), "gain")}
+
+    def bind(self, tensors, dtype, device):
+        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.eps = float(self.param("eps"))
+        self.mult = float(self.spec.params.get("mult", 1.0))
+        self.dtype = dtype
+
+    def add_branch(self, stream: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+        """Adds the normed branch to the fp32 ``stream`` in place; returns the stream's copy in the
+        compute dtype (the stream itself for float32)."""
+        if isinstance(y, BranchSum):
+            y = y.total()
+        return ops.scaled_norm_add(stream, y, self.weight, self.eps, self.mult, self.dtype)
+
+    def forward(self, x, residual, rows=None):
+        raise RuntimeError("this norm stands behind a branch; the arrangement calls add_branch")
+
+
+def stream_and_copy(x, residual, dtype: torch.dtype):
+    """``(fp32 stream, its copy in the compute dtype)`` from what a layer is handed: a ``StreamCopy`` beside
+    the stream, the embedding's output before the first layer, or addends that are still to be added."""
+    if isinstance(x, StreamCopy) and residual is not None and x.rounded is not None:
+        return residual, x.rounded
+    if residual is None:
+        if isinstance(x, BranchSum):
+            x = x.total()
+        stream = x if x.dtype == torch.float32 else x.to(torch.float32)
+        return stream, (x if x.dtype == dtype else ops.scaled_norm_add(stream, None, None, 0.0, 1.0, dtype))
+    if isinstance(x, BranchSum):
+        x = x.total() if len(x) or x.stream_add is not None or x.row_add is not None else None
+    if x is not None:
+        residual = residual + x.to(torch.float32)
+    return residual, ops.scaled_norm_add(residual, None, None, 0.0, 1.0, dtype)
+
+
 class NoNorm(Norm):
     """The place of a norm in a layer that has nothing behind it (a layer without a feed-forward)."""
 
@@ -222,6 +270,27 @@ def rotary_inv_freq(head_dim: int, theta: float, rotary_dim: int | None = None,
     return torch.where(in_between, blended, slowed)
 
 
+def rotary_freq64(over: int, theta: float, rotary_dim: int, scaling: dict | None) -> torch.Tensor:
+    """The same frequencies in float64 from end to end (``theta^(-2i / over)`` for ``i < rotary_dim / 2``, with
+    the three bands of the rescale where ``scaling`` is given), for kernels that form the angle in double
+    precision."""
+    out = []
+    for i in range(rotary_dim // 2):
+        f = float(theta) ** (-2.0 * i / over)
+        if scaling is not None:
+            slow_down = float(scaling["factor"])
+            low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+            context = float(scaling["original_max_position_embeddings"])
+            wave = 2.0 * math.pi / f
+            if wave > context / low:
+                f = f / slow_down
+            elif not wave < context / high:
+                blend = (context / wave - low) / (high - low)
+                f = (1.0 - blend) * f / slow_down + blend * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float64)
+
+
 class RotaryPosition(Position):
     """Rotary encoding, half layout: dim ``j`` pairs with ``j + rotary_dim/2``
     (reference ``models/blocks/rope.py:392-431``).  Angles ``p * inv_freq`` and their sine
@@ -247,11 +316,8 @@ class RotaryPosition(Position):
         self.inv_freq = rotary_inv_freq(
             over, float(self.param("theta")), self.rotary_dim, self.spec.params.get("scaling")
         ).to(device)
-        if self.spec.params.get("scaling") is None:
-            i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-            self.freq64 = (float(self.param("theta")) ** (-2.0 * i / over)).to(device)
-        else:
-            self.freq64 = self.inv_freq.to(torch.float64)
+        self.freq64 = rotary_freq64(over, float(self.param("theta")), self.rotary_dim,
+                                    self.spec.params.get("scaling")).to(device)
         # layers with the same frequencies share one table per step
         self._table_key = (d, self.rotary_dim, float(self.param("theta")), repr(self.spec.params.get("scaling")), span)
 
@@ -501,7 +567,8 @@ class OutputHead(Part):
     """``logits = z W^T`` in fp32 (reference ``models/llama/llama.py:169-172``).  With
     ``tied`` the embedding's table is the weight and no tensor of its own is expected.
 
-    params: ``vocab_size``, ``hidden_size``, ``tied``.  tensors: ``weight`` unless tied.
+    params: ``vocab_size``, ``hidden_size``, ``tied``, optional ``scale`` (the logits are multiplied by it,
+    in fp32).  tensors: ``weight`` unless tied.
     """
 
     @property
@@ -522,7 +589,11 @@ class OutputHead(Part):
             self.proj = Linear(_as_compute(tensors["weight"], dtype).contiguous())
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        return self.proj(z, out_dtype=torch.float32)
+        logits = self.proj(z, out_dtype=torch.float32)
+        scale = self.spec.params.get("scale")
+        if scale is not None and float(scale) != 1.0:
+            ops.scale_(logits, float(scale))
+        return logits
 
 
 # ----------------------------------------------------------------------------- arrangement
@@ -602,6 +673,61 @@ class ParallelBlock(Arrangement):
         return BranchSum((m, f)), stream
 
 
+class BranchNormBlock(Arrangement):
+    """``h += norm1(mixer(h)); h += norm2(ffn(h))``: both branches read the stream itself (its copy in
+    the compute dtype) and each norm, a ``BranchRMSNorm`` with the residual factor in it, stands behind
+    its branch.  The fp32 stream is updated in place; the block hands on a ``StreamCopy``.  A layer
+    without a feed-forward (``no_feed_forward``) is the mixer's half alone."""
+
+    def forward(self, x, residual, ctx, cache):
+        stream, h = stream_and_copy(x, residual, ctx.dtype)
+        h = self.mixer_norm.add_branch(stream, self.mixer.forward(h, ctx, cache, self.position))
+        if not isinstance(self.feed_forward, NoFeedForward):
+            h = self.feed_forward_norm.add_branch(stream, self.feed_forward.forward(h, ctx))
+        return StreamCopy.of(h), stream
+
+
+class TokenSideInput(StreamPart):
+    """What a layer takes from the token itself, behind its branches: with ``e`` the columns ``[index *
+    dim, (index + 1) * dim)`` of the token's row of a table shared by all layers, ``g = gelu_tanh(W_gate h)
+    * e``, ``y = W_proj g``, and the stream takes ``mult * w * y * rsqrt(mean(y^2) + eps)``, an RMS norm
+    with a plain gain (``h``: the stream's copy in the compute dtype; the gate's pre-activations, the
+    norm and the sum are fp32).
+
+    params: ``hidden_size``, ``vocab_size``, ``dim``, ``index``, ``table_width``, ``eps``, optional ``mult``.
+    tensors: ``table [vocab_size, table_width]``, ``gate [dim, hidden_size]``, ``proj [hidden_size, dim]``,
+    ``norm [hidden_size]``.
+    """
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden, self.dim = int(self.param("hidden_size")), int(self.param("dim"))
+        self.col0 = int(self.spec.params.get("index", 0)) * self.dim
+        self.table_width = int(self.param("table_width"))
+        if self.dim <= 0 or self.col0 < 0 or self.col0 + self.dim > self.table_width:
+            raise ValueError(f"columns {self.col0}..{self.col0 + self.dim} of a table row of {self.table_width}")
+
+    def param_decls(self):
+        return {"table": ParamDecl((int(self.param("vocab_size")), self.table_width)),
+                "gate": ParamDecl((self.dim, self.hidden)), "proj": ParamDecl((self.hidden, self.dim)),
+                "norm": ParamDecl((self.hidden,), "gain")}
+
+    def bind(self, tensors, dtype, device):
+        # this layer's columns only: the layers' copies together are one table
+        self.table = _as_compute(tensors["table"], dtype)[:, self.col0:self.col0 + self.dim].contiguous()
+        self.gate = Linear(_as_compute(tensors["gate"], dtype).contiguous())
+        self.proj = Linear(_as_compute(tensors["proj"], dtype).contiguous())
+        self.gain = tensors["norm"].to(torch.float32).contiguous()
+        self.eps, self.mult = float(self.param("eps")), float(self.spec.params.get("mult", 1.0))
+        self.dtype = dtype
+
+    def forward(self, x, residual, ctx, embedded):
+        stream, h = stream_and_copy(x, residual, self.dtype)
+        g = ops.token_gate(self.gate(h, out_dtype=torch.float32), self.table, ctx.token_ids, 0)
+        h = ops.scaled_norm_add(stream, self.proj(g), self.gain, self.eps, self.mult, self.dtype)
+        return StreamCopy.of(h), stream
+
+
 class NoFeedForward(FeedForward):
     """A layer without a feed-forward."""
 
@@ -612,6 +738,9 @@ class NoFeedForward(FeedForward):
 register_norm("rmsnorm", RMSNorm, replace=True)
 register_norm("layernorm", LayerNorm, replace=True)
 register_norm("no_norm", NoNorm, replace=True)
+register_norm("branch_rmsnorm", BranchRMSNorm, replace=True)
+register_arrangement("branch_norm", BranchNormBlock, replace=True)
+register_stream_part("token_side_input", TokenSideInput, replace=True)
 register_norm("same_norm", SameNorm, replace=True)
 register_position("rotary_interleaved", InterleavedRotary, replace=True)
 register_feed_forward("no_feed_forward", NoFeedForward, replace=True)

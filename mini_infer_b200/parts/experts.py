@@ -15,19 +15,24 @@ class RoutedExperts(FeedForward):
     """Router logits ``z = W_r h`` in fp32; a token's ``top`` experts are those with the largest
     logits and their weights the softmax over those logits alone (``scores`` ``"chosen"``, the
     default), or their scores under the softmax over all experts, divided by the sum of these
-    (+ 1e-20) and multiplied by ``route_scale`` (``scores`` ``"all"``).  With ``groups`` > 1 the experts
-    form that many equal groups of neighbours, a group counts as its best expert, and only experts of
-    the ``keep_groups`` best groups can be chosen.  The output is the weighted sum of the chosen
-    experts' outputs, plus the shared expert's where there is one.  An expert is
+    (+ 1e-20) and multiplied by ``route_scale`` (``scores`` ``"all"``), or (``scores`` ``"sigmoid"``) the
+    scores are ``s = sigmoid(z)``, the choice goes by ``s + correction`` (``correction``: a tensor, one number
+    per expert) and the weights are the chosen ``s`` times ``route_scale``, not renormalised.  With
+    ``groups`` > 1 the experts form that many equal groups of neighbours, a group counts as its best
+    expert (``group_score`` ``"best"``, the default) or as the sum of its two best choice scores
+    (``"top2"``), and only experts of the ``keep_groups`` best groups can be chosen.  The output is the
+    weighted sum of the chosen experts' outputs, plus the shared expert's where there is one, which
+    ``shared_gate`` ``"sigmoid"`` multiplies by ``sigmoid(w_sg . h)``, one number per token.  An expert is
     ``W_down (g' * sigmoid(alpha g') * (u' + 1))`` with ``g' = min(W_gate h, limit)`` and
     ``u' = clamp(W_up h, -limit, limit)`` (``activation`` ``"clamped"``, the default), or
     ``W_down (silu(W_gate h) * W_up h)`` (``"silu"``), no biases.
 
     params: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit`` (with the clamped activation),
     optional ``alpha`` (default 1.702), ``shared_ff`` (0 or absent: no shared expert), ``shared_limit``,
-    ``activation``, ``scores``, ``route_scale`` (default 1), ``groups`` and ``keep_groups``.
-    tensors: ``router``, ``e{i}.gate``, ``e{i}.up``, ``e{i}.down`` and, with a shared expert,
-    ``shared.gate``, ``shared.up``, ``shared.down``.
+    ``activation``, ``scores``, ``route_scale`` (default 1), ``groups``, ``keep_groups``, ``group_score``,
+    ``correction`` (default False) and ``shared_gate``.
+    tensors: ``router``, ``e{i}.gate``, ``e{i}.up``, ``e{i}.down``, with a correction ``correction`` and, with a
+    shared expert, ``shared.gate``, ``shared.up``, ``shared.down`` and, with its gate, ``shared.sg``.
     """
 
     def __init__(self, spec):
@@ -44,12 +49,23 @@ class RoutedExperts(FeedForward):
         else:
             raise ValueError(f"unknown activation {self.activation!r} of the experts: 'clamped' or 'silu'")
         self.scores = str(g("scores", "chosen"))
-        if self.scores not in ("chosen", "all"):
-            raise ValueError(f"unknown scores {self.scores!r} of the router: 'chosen' or 'all'")
+        if self.scores not in ops.ROUTE_MODES:
+            raise ValueError(f"unknown scores {self.scores!r} of the router: one of {sorted(ops.ROUTE_MODES)}")
+        self.correction = bool(g("correction", False))
+        if self.correction and self.scores != "sigmoid":
+            raise ValueError("a correction of the choice goes with sigmoid scores")
+        self.group_score = str(g("group_score", "best"))
+        if self.group_score not in ("best", "top2"):
+            raise ValueError(f"unknown group_score {self.group_score!r}: 'best' or 'top2'")
+        self.shared_gate = g("shared_gate")
+        if self.shared_gate not in (None, "sigmoid"):
+            raise ValueError(f"unknown shared_gate {self.shared_gate!r}: 'sigmoid' or none")
         self.route_scale = float(g("route_scale", 1.0))
         self.groups, self.keep_groups = int(g("groups") or 0), int(g("keep_groups") or 0)
         self.shared_ff = int(g("shared_ff") or 0)
         self.shared_limit = float(g("shared_limit", self.limit))
+        if self.shared_gate and not self.shared_ff:
+            raise ValueError("a gate of the shared expert without a shared expert")
         if not 0 < self.top <= self.experts:
             raise ValueError(f"{self.top} of {self.experts} experts per token")
         if self.groups > 1:
@@ -69,11 +85,18 @@ class RoutedExperts(FeedForward):
             decls["shared.gate"] = ParamDecl((self.shared_ff, H))
             decls["shared.up"] = ParamDecl((self.shared_ff, H))
             decls["shared.down"] = ParamDecl((H, self.shared_ff))
+            if self.shared_gate:
+                decls["shared.sg"] = ParamDecl((1, H))
+        if self.correction:
+            decls["correction"] = ParamDecl((self.experts,), "table")
         return decls
 
     def bind(self, tensors, dtype, device):
         E = range(self.experts)
         self.router = _as_compute(tensors["router"], dtype).contiguous()
+        if self.shared_gate:     # the gate's row rides in the router's product: its logit comes out in fp32 beside theirs
+            self.router = torch.cat([self.router, _as_compute(tensors["shared.sg"], dtype).reshape(1, -1)]).contiguous()
+        self.choice_correction = tensors["correction"].to(torch.float32).contiguous() if self.correction else None
         # per expert its gate rows, then its up rows: one operand for a grouped product, two for the own kernels
         self.w_gate_up = torch.stack([torch.cat([_as_compute(tensors[f"e{e}.gate"], dtype),
                                                  _as_compute(tensors[f"e{e}.up"], dtype)]) for e in E]).contiguous()
@@ -89,10 +112,13 @@ class RoutedExperts(FeedForward):
         if self.shared_in is not None:
             limit = self.shared_limit if self.activation == "clamped" else self.limit
             shared = self.shared_out(ops.clamped_glu(self.shared_in(x), limit, self.alpha, self.up_offset))
-        ids, weights = ops.moe_route(x, self.router, self.top, all_scores=self.scores == "all", groups=self.groups,
-                                     keep_groups=self.keep_groups, scale=self.route_scale)
+        ids, weights, logits = ops.moe_route(x, self.router, self.top, scores=self.scores, groups=self.groups,
+                                             keep_groups=self.keep_groups, scale=self.route_scale,
+                                             correction=self.choice_correction, group_top2=self.group_score == "top2",
+                                             experts=self.experts, return_logits=True)
+        gate = logits[:, self.experts:] if self.shared_gate else None
         return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit, self.alpha, shared,
-                               up_offset=self.up_offset)
+                               up_offset=self.up_offset, shared_gate=gate)
 
 
 register_feed_forward("routed_experts", RoutedExperts, replace=True)

@@ -1,9 +1,10 @@
 """Mixers beyond plain grouped-query attention: a sliding-window attention with unit-norm queries
 and keys and gated heads, an attention over chunks of positions with normed queries and keys,
-blended values and a gate per head, four recurrent mixers that keep a state of fixed size per
-request (the real-gated linear recurrent unit, gated linear attention, retention with a fixed decay
-per head, and the gated delta rule with a decay per key channel), and a mixer that runs two of them
-side by side on the same input.
+blended values and a gate per head (also with biases, a learned sink per head, or another layer's keys
+and values), five recurrent mixers that keep a state of fixed size per request (the real-gated linear
+recurrent unit, gated linear attention, retention with a fixed decay per head, the gated delta rule
+with a decay per key channel, and a matrix memory with scalar gates and a running maximum), and a
+mixer that runs two of them side by side on the same input.
 
 They share one shape (``ProjectedMixer``): everything a mixer projects from its input is one
 stacked matrix, everything it hands to its output projection is one row of activations.  A mixer
@@ -31,12 +32,17 @@ class ProjectedMixer(Mixer):
     ``self.w_in [in_width, H]`` and ``self.w_out [H, out_width]`` in ``bind``, and implement
     ``mix(proj, out, out_scale, ctx, cache, position)``, which reads the projected row ``proj
     [M, in_width]`` (a column range; it may be overwritten) and writes ``out [M, out_width]``
-    (a column range) times ``out_scale``."""
+    (a column range) times ``out_scale``.  A mixer that needs some products of its input unrounded
+    (the gates of a recurrence) builds ``self.w_in32 [in32_width, H]`` too; ``mix`` then gets them as
+    ``proj32`` (fp32, a column range)."""
 
     in_width: int
     out_width: int
     w_in: torch.Tensor
     w_out: torch.Tensor
+    in32_width: int = 0
+    w_in32: torch.Tensor | None = None
+    takes_position: bool = True       # side by side with another mixer: whether the layer's position part is for this one
 
     def mix(self, proj: torch.Tensor, out: torch.Tensor, out_scale: float, ctx: StepContext, cache: LayerCache,
             position) -> None:
@@ -44,11 +50,15 @@ class ProjectedMixer(Mixer):
 
     def finish_bind(self) -> None:
         self._in, self._out = Linear(self.w_in), Linear(self.w_out)
+        self._in32 = Linear(self.w_in32) if self.in32_width else None
 
     def forward(self, x, ctx, cache, position):
         proj = self._in(x)
         out = torch.empty((ctx.n_tokens, self.out_width), dtype=x.dtype, device=x.device)
-        self.mix(proj, out, 1.0, ctx, cache, position)
+        if self._in32 is None:
+            self.mix(proj, out, 1.0, ctx, cache, position)
+        else:
+            self.mix(proj, out, 1.0, ctx, cache, position, proj32=self._in32(x, out_dtype=torch.float32))
         return self._out(out)
 
 
@@ -180,13 +190,18 @@ class ChunkAttention(ProjectedMixer):
     run become ``(1 - lam) v + lam v_first`` (``lam`` the layer's ``vmix``, ``v_first`` the first such
     layer's values of the same token); the blended values are what is cached; ``value_blend: "source"`` marks a layer that
     only gives its values away and has no ``vmix``.  With ``head_gate`` head
-    ``h``'s output is multiplied by ``sigmoid(W_g x)_h``, one number per head.  Scores, weights and sums
-    are fp32 for either dtype.
+    ``h``'s output is multiplied by ``sigmoid(W_g x)_h``, one number per head.  With ``bias`` q, k and v
+    have biases (added in fp32 before the norm).  With ``sink`` ``"learned"`` the softmax's denominator of head
+    ``h`` also holds ``exp(sink_h)``, a number that has no key and no value and is not scaled.  With
+    ``own_kv`` False the layer has no keys and values of its own (no ``k``, ``v``, ``k.norm``, no biases of
+    theirs): it reads the cache layer that another layer with the same head counts wrote, with its own
+    queries.  Scores, weights and sums are fp32 for either dtype.
 
     params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``; optional ``value_dim``
-    (default ``head_dim``), ``chunk``, ``qk_norm`` (default False) with ``eps``, ``value_blend`` and
-    ``head_gate`` (default False).
-    tensors: ``q``, ``k``, ``v``, ``o`` and, as asked, ``q.norm``, ``k.norm``, ``vmix``, ``g``.
+    (default ``head_dim``), ``chunk``, ``qk_norm`` (default False) with ``eps``, ``value_blend``,
+    ``head_gate``, ``bias`` (default False), ``sink`` (None or ``"learned"``) and ``own_kv`` (default True).
+    tensors: ``q``, ``k``, ``v``, ``o`` and, as asked, ``q.norm``, ``k.norm``, ``vmix``, ``g``, ``q.b``, ``k.b``,
+    ``v.b``, ``sink``.
     """
 
     def __init__(self, spec):
@@ -206,22 +221,39 @@ class ChunkAttention(ProjectedMixer):
         self.value_blend = blend is True            # takes ``vmix`` and blends (unless it is the first to run)
         self.value_source = bool(blend)             # may leave its values for the layers behind it
         self.head_gate = bool(g("head_gate", False))
+        self.bias = bool(g("bias", False))
+        self.sink = g("sink")
+        self.own_kv = bool(g("own_kv", True))
+        if self.sink not in (None, "learned"):
+            raise ValueError(f"unknown sink {self.sink!r}: 'learned' or none")
+        if not self.own_kv and (self.value_source or self.chunk):
+            raise ValueError("a layer without keys and values of its own neither blends values nor has chunks")
         if self.nq % self.nkv:
             raise ValueError(f"{self.nq} query heads cannot share {self.nkv} key/value heads")
         if not (0 < self.d <= 1024 and 0 < self.dv <= 512):
             raise ValueError(f"head sizes {self.d} (keys, up to 1024) and {self.dv} (values, up to 512)")
+        own = self.nkv if self.own_kv else 0           # key/value heads that this layer projects
         self.q_off, self.k_off = 0, self.nq * self.d
-        self.v_off = self.k_off + self.nkv * self.d
-        self.g_off = self.v_off + self.nkv * self.dv
+        self.v_off = self.k_off + own * self.d
+        self.g_off = self.v_off + own * self.dv
         self.in_width = self.g_off + (self.nq if self.head_gate else 0)
         self.out_width = self.nq * self.dv
 
     def param_decls(self):
         H, nq, nkv, d, dv = self.hidden, self.nq, self.nkv, self.d, self.dv
-        decls = {"q": ParamDecl((nq * d, H)), "k": ParamDecl((nkv * d, H)), "v": ParamDecl((nkv * dv, H)),
-                 "o": ParamDecl((H, nq * dv))}
+        decls = {"q": ParamDecl((nq * d, H)), "o": ParamDecl((H, nq * dv))}
+        if self.own_kv:
+            decls["k"], decls["v"] = ParamDecl((nkv * d, H)), ParamDecl((nkv * dv, H))
         if self.qk_norm:
-            decls["q.norm"], decls["k.norm"] = ParamDecl((d,), "gain"), ParamDecl((d,), "gain")
+            decls["q.norm"] = ParamDecl((d,), "gain")
+            if self.own_kv:
+                decls["k.norm"] = ParamDecl((d,), "gain")
+        if self.bias:
+            decls["q.b"] = ParamDecl((nq * d,), "table")
+            if self.own_kv:
+                decls["k.b"], decls["v.b"] = ParamDecl((nkv * d,), "table"), ParamDecl((nkv * dv,), "table")
+        if self.sink:
+            decls["sink"] = ParamDecl((nq,), "table")
         if self.value_blend:
             decls["vmix"] = ParamDecl((), "table")
         if self.head_gate:
@@ -245,26 +277,28 @@ class ChunkAttention(ProjectedMixer):
         """bfloat16 with sizes the tensor-core kernels take and aligned rows: those kernels (the balanced
         decode kernel, tcgen05 or mma.sync for prompt portions; scores and softmax in fp32, as everywhere);
         else the kernel for keys and values of two sizes or the CUDA-core kernel."""
-        if (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0 and heads.is_contiguous()
-                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        if (self.sinks is None and q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0
+                and heads.is_contiguous() and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
             ops.attention(q, q.stride(0), heads, cache, ctx, self.nq, self.nkv, self.d, self.scale,
                           chunk=self.chunk or 0)
         else:
             ops.attention_ext(q, heads, cache, ctx, self.nq, self.nkv, self.d, self.dv, self.scale,
-                              chunk=self.chunk or 0)
+                              chunk=self.chunk or 0, sinks=self.sinks)
 
     def bind(self, tensors, dtype, device):
-        names = ["q", "k", "v"] + (["g"] if self.head_gate else [])
+        names = ["q"] + (["k", "v"] if self.own_kv else []) + (["g"] if self.head_gate else [])
         self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in names], dim=0).contiguous()
         self.w_out = _as_compute(tensors["o"], dtype).contiguous()
         self.q_gain = _f32(tensors["q.norm"]) if self.qk_norm else None
-        self.k_gain = _f32(tensors["k.norm"]) if self.qk_norm else None
+        self.k_gain = _f32(tensors["k.norm"]) if self.qk_norm and self.own_kv else None
+        self.sinks = _f32(tensors["sink"]) if self.sink else None
+        self.in_bias = None
+        if self.bias:        # one number per packed column of q, k and v
+            self.in_bias = torch.cat([_f32(tensors[n + ".b"]) for n in (["q", "k", "v"] if self.own_kv else ["q"])])
         self.blend = _f32(tensors["vmix"]).reshape(1) if self.value_blend else None
         self.finish_bind()
 
     def mix(self, proj, out, out_scale, ctx, cache, position):
-        if out_scale != 1.0:
-            raise ValueError("this attention cannot scale its output")
         nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
         rot, freq = _half_rotation(position, d)
         v_other = None
@@ -281,18 +315,25 @@ class ChunkAttention(ProjectedMixer):
             else:
                 v_other = first
         group = ctx.groups[cache.group]
-        ops.qk_norm_rope_store(proj, self.q_off, self.k_off, self.v_off, nq, nkv, d, dv, q_gain=self.q_gain,
-                               k_gain=self.k_gain, eps=self.eps, rot=rot, positions=ctx.positions, freq=freq,
-                               v_other=v_other, blend=self.blend if v_other is not None else None,
+        if self.own_kv != bool(cache.writes):
+            raise ValueError("a layer with keys and values of its own writes its cache layer; one without reads another's")
+        own = nkv if self.own_kv else 0
+        ops.qk_norm_rope_store(proj, self.q_off, self.k_off, self.v_off if own else None, nq, own, d, dv,
+                               q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps, rot=rot, positions=ctx.positions,
+                               freq=freq, v_other=v_other, blend=self.blend if v_other is not None else None,
                                slots=group.slots if cache.writes else None,
-                               kcache=cache.k if cache.writes else None, vcache=cache.v if cache.writes else None)
+                               kcache=cache.k if cache.writes else None, vcache=cache.v if cache.writes else None,
+                               bias=self.in_bias)
         q = proj[:, self.q_off:self.q_off + nq * d]
-        if not self.head_gate:
+        if not self.head_gate and out_scale == 1.0:
             self._attend(q, out, cache, ctx)
             return
         heads = torch.empty((ctx.n_tokens, nq * dv), dtype=proj.dtype, device=proj.device)
         self._attend(q, heads, cache, ctx)
-        ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq], out, "sigmoid", 1.0, per=dv)
+        if self.head_gate:
+            ops.gate_mul(heads, proj[:, self.g_off:self.g_off + nq], out, "sigmoid", out_scale, per=dv)
+        else:
+            ops.gate_mul(heads, None, out, None, out_scale)
 
 # ----------------------------------------------------------------------------- gated linear attention
 
@@ -521,6 +562,76 @@ class ChannelDeltaRule(ProjectedMixer):
                            taps=self.taps)
         ops.headnorm_gate(o, self.norm_gain, gate, out, self.heads, self.dv, self.eps, "sigmoid", out_scale)
 
+# ----------------------------------------------------------------------------- matrix memory with scalar gates
+
+
+class MatrixMemory(ProjectedMixer):
+    """A matrix memory with an input and a forget gate per head and a running maximum that keeps their
+    exponentials in range.  ``q = W_q h * key_dim^-1/2``, ``k = W_k h``, ``v = W_v h``; per head the log gates
+    ``i = cap tanh((W_i h + b_i) / cap)`` and ``f = logsigmoid(cap tanh((W_f h + b_f) / cap))``.  From ``S = 0``,
+    ``n = 0``, ``m = 0``:  ``m' = max(f + m, i)``,  ``S' = exp(f + m - m') S + exp(i - m') k v^T``,  ``n'`` likewise
+    with ``k`` alone,  ``o = S'^T q / (max(|n' . q|, exp(-m')) + den_eps)``.  Each head's ``o`` is divided by its
+    root mean square over ``value_dim``; the heads are multiplied by a gain (one number per head and
+    channel) and by ``sigmoid(W_g h)``, and projected.  The state (fp32, per request) is ``[S | n]`` as
+    ``[heads, key_dim, value_dim + 1]``, then ``m [heads]``; gates, exponentials and the state are fp32 and
+    the gates' pre-activations come from a product of their own with an fp32 result.
+
+    params: ``hidden_size``, ``num_heads``, ``key_dim``, ``value_dim``, ``gate_cap``, ``eps``, optional
+    ``den_eps`` (default 1e-6).
+    tensors: ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``, ``i``, ``i.b``, ``f``, ``f.b``.
+    """
+
+    takes_position = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.param("hidden_size"))
+        self.heads = int(self.param("num_heads"))
+        self.dk, self.dv = int(self.param("key_dim")), int(self.param("value_dim"))
+        self.cap = float(self.param("gate_cap"))
+        self.eps = float(self.param("eps"))
+        self.den_eps = float(self.spec.params.get("den_eps", 1e-6))
+        if not 0 < self.dk <= 256:
+            raise ValueError(f"key size {self.dk} must lie in [1, 256]")
+        if not self.cap > 0:
+            raise ValueError(f"the gates' cap must be positive, got {self.cap}")
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        self.q_off, self.k_off, self.v_off, self.g_off = 0, hk, 2 * hk, 2 * hk + hv
+        self.in_width = 2 * hk + 2 * hv
+        self.in32_width = 2 * self.heads
+        self.out_width = hv
+        self.m_offset = self.heads * self.dk * (self.dv + 1)
+
+    def param_decls(self):
+        H, hk, hv, n = self.hidden, self.heads * self.dk, self.heads * self.dv, self.heads
+        return {"q": ParamDecl((hk, H)), "k": ParamDecl((hk, H)), "v": ParamDecl((hv, H)), "g": ParamDecl((hv, H)),
+                "o": ParamDecl((H, hv)), "norm": ParamDecl((hv,), "gain"),
+                "i": ParamDecl((n, H)), "i.b": ParamDecl((n,), "table"),
+                "f": ParamDecl((n, H)), "f.b": ParamDecl((n,), "table")}
+
+    def state_need(self):
+        return StateNeed((self.m_offset + self.heads,), torch.float32)
+
+    def bind(self, tensors, dtype, device):
+        self.w_in = torch.cat([_as_compute(tensors[n], dtype) for n in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_in32 = torch.cat([_as_compute(tensors["i"], dtype), _as_compute(tensors["f"], dtype)], dim=0).contiguous()
+        self.w_out = _as_compute(tensors["o"], dtype).contiguous()
+        self.bias_i, self.bias_f = _f32(tensors["i.b"]), _f32(tensors["f.b"])
+        self.norm_gain = _f32(tensors["norm"])
+        self.finish_bind()
+
+    def mix(self, proj, out, out_scale, ctx, cache, position, proj32=None):
+        if position is not None:
+            raise ValueError("this mixer takes no position part: the order of the tokens is in its state")
+        hk, hv = self.heads * self.dk, self.heads * self.dv
+        gates = ops.mlstm_gates(proj32, self.bias_i, self.bias_f, self.cap, self.heads, cache.state, self.m_offset, ctx)
+        o = ops.gla_scan(proj[:, self.q_off:self.q_off + hk], proj[:, self.k_off:self.k_off + hk],
+                         proj[:, self.v_off:self.v_off + hv], None, None, 1.0, self.dk ** -0.5, self.heads, self.dk,
+                         self.dv, cache.state, ctx, tok_gates=gates, extra_col=True)
+        ops.headnorm_gate(o, self.norm_gain, proj[:, self.g_off:self.g_off + hv], out, self.heads, self.dv, self.eps,
+                          "sigmoid", out_scale, tok_gates=gates, den_eps=self.den_eps)
+
+
 # ----------------------------------------------------------------------------- real-gated linear recurrent unit
 
 
@@ -630,15 +741,23 @@ class SideBySide(Mixer):
             c.bind({local: tensors[c.spec.prefix + local] for local in c.param_decls()}, dtype, device)
         self._in = Linear(torch.cat([c.w_in for c in self.children], dim=0).contiguous())
         self._out = Linear(torch.cat([c.w_out for c in self.children], dim=1).contiguous())
+        rows32 = [c.w_in32 for c in self.children if c.in32_width]
+        self._in32 = Linear(torch.cat(rows32, dim=0).contiguous()) if rows32 else None
         for c in self.children:      # the stacked copies are the ones that run
-            c.w_in = c.w_out = c._in = c._out = None
+            c.w_in = c.w_out = c._in = c._out = c.w_in32 = c._in32 = None
 
     def forward(self, x, ctx, cache, position):
         proj = self._in(x)
+        proj32 = self._in32(x, out_dtype=torch.float32) if self._in32 is not None else None
         out = torch.empty((ctx.n_tokens, sum(c.out_width for c in self.children)), dtype=x.dtype, device=x.device)
-        i0 = o0 = 0
+        i0 = o0 = p0 = 0
         for c, scale in zip(self.children, self.scales):
-            c.mix(proj[:, i0:i0 + c.in_width], out[:, o0:o0 + c.out_width], scale, ctx, cache, position)
+            kw = {}
+            if c.in32_width:
+                kw["proj32"] = proj32[:, p0:p0 + c.in32_width]
+                p0 += c.in32_width
+            c.mix(proj[:, i0:i0 + c.in_width], out[:, o0:o0 + c.out_width], scale, ctx, cache,
+                  position if c.takes_position else None, **kw)
             i0 += c.in_width
             o0 += c.out_width
         return self._out(out)
@@ -650,4 +769,6 @@ register_mixer("rglru", RealGatedLinearRecurrence, replace=True)
 register_mixer("chunk_attention", ChunkAttention, replace=True)
 register_mixer("retention", Retention, replace=True)
 register_mixer("channel_delta_rule", ChannelDeltaRule, replace=True)
+register_mixer("matrix_memory", MatrixMemory, replace=True)
+register_mixer("normed_attention", ChunkAttention, replace=True)
 register_mixer("side_by_side", SideBySide, replace=True)

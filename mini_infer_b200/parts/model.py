@@ -64,7 +64,10 @@ class DecoderModel:
         # stream parts that run before a schedule entry (None where an entry has none)
         self.before: list[Part | None] = [build_part("stream", e.before) if e.before is not None else None
                                           for e in spec.schedule]
-        self._keeps_embedding = any(getattr(p, "needs_embedding", False) for p in self.before if p is not None)
+        self.after: list[Part | None] = [build_part("stream", e.after) if e.after is not None else None
+                                         for e in spec.schedule]
+        self._keeps_embedding = any(getattr(p, "needs_embedding", False) for p in self.before + self.after
+                                    if p is not None)
         self._bound = False
 
     # ------------------------------------------------------------------ declarations
@@ -74,6 +77,7 @@ class DecoderModel:
         for b in self.blocks:
             parts.extend(b.parts())
         parts.extend(p for p in self.before if p is not None)
+        parts.extend(p for p in self.after if p is not None)
         parts.extend([self.final_norm, self.head])
         return parts
 
@@ -154,7 +158,7 @@ class DecoderModel:
         for b in self.blocks:
             for part in b.parts():
                 part.bind(local_view(part), dtype, device)
-        for part in self.before:
+        for part in self.before + self.after:
             if part is not None:
                 part.bind(local_view(part), dtype, device)
         self.final_norm.bind(local_view(self.final_norm), dtype, device)
@@ -184,10 +188,15 @@ class DecoderModel:
             block = self.blocks[entry.layer]
             if block.entry() is None:
                 x, residual = block.forward(x, residual, ctx, cache)
-                continue
-            # a layer that takes part in the hand-over of norms is told how the next one begins
-            after = self.blocks[self.schedule[i + 1].layer].entry() if i + 1 < len(self.schedule) else None
-            x, residual = block.forward(x, residual, ctx, cache, following=after)
+            else:
+                # a layer that takes part in the hand-over of norms is told how the next one begins
+                # (not across a stream part behind this layer, which wants a plain stream)
+                nxt = None
+                if i + 1 < len(self.schedule) and self.after[i] is None:
+                    nxt = self.blocks[self.schedule[i + 1].layer].entry()
+                x, residual = block.forward(x, residual, ctx, cache, following=nxt)
+            if self.after[i] is not None:
+                x, residual = self.after[i].forward(x, residual, ctx, embedded)
         if n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
         z, _ = self.final_norm.forward(x, residual, rows=want_rows)

@@ -10,7 +10,8 @@ descriptions; no part ever sees the configuration or knows which model it is in.
 weights), the cache layer it uses, and whether it writes that cache.  A layer
 may appear twice (shared weights, each run with a cache layer of its own), and
 a layer may read a cache layer that another layer wrote
-(``writes_cache=False``).  An entry may name a stream part that runs before it (``before``).
+(``writes_cache=False``).  An entry may name a stream part that runs before it (``before``) and one that
+runs after it (``after``).
 """
 
 from __future__ import annotations
@@ -56,12 +57,14 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """``before``: a registered stream part that works on the residual stream right before this
-    entry's layer runs (what a model adds to the stream between two stretches of layers)."""
+    entry's layer runs (what a model adds to the stream between two stretches of layers); ``after``: one
+    that works on it right after the layer (what a layer adds beside its mixer and feed-forward)."""
 
     layer: int
     cache: int
     writes_cache: bool = True
     before: PartSpec | None = None
+    after: PartSpec | None = None
 
 
 @dataclass(frozen=True)
