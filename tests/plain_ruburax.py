@@ -202,32 +202,43 @@ def gated_unit(h: torch.Tensor, W: dict, prefix: str = "") -> torch.Tensor:
 def choose_experts(z: torch.Tensor, correction: torch.Tensor, router: dict):
     """One token: scores ``s = sigmoid(z)``, choice scores ``s + correction``.  With groups, a group's score
     is the sum of its two largest choice scores and only experts of the best ``keep`` groups stay in the
-    race.  Returns the ``top`` experts by choice score and their weights ``s * scale`` (not renormalised)."""
+    race.  Returns the ``top`` experts by choice score, their weights ``s * scale`` (not renormalised), and
+    how close the call was: the smallest gap between something taken and something left (groups, experts)."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(z)
     choice = s + correction
     allowed = torch.ones(E, dtype=torch.bool)
+    margin = math.inf
     groups = router.get("groups")
     if groups and int(groups["count"]) > 1:
         n, keep = int(groups["count"]), int(groups["keep"])
         per = E // n
         score = torch.stack([torch.topk(choice[g * per:(g + 1) * per], min(2, per)).values.sum() for g in range(n)])
+        order = torch.sort(score, descending=True).values
+        if keep < n:
+            margin = float(order[keep - 1] - order[keep])
         kept = torch.topk(score, keep).indices.tolist()
         allowed[:] = False
         for g in kept:
             allowed[g * per:(g + 1) * per] = True
     masked = torch.where(allowed, choice, torch.full_like(choice, -math.inf))
     ids = torch.topk(masked, top).indices
-    return ids.tolist(), (s[ids] * float(router["scale"])).tolist()
+    order = torch.sort(masked, descending=True).values
+    if top < E and order[top] > -math.inf:
+        margin = min(margin, float(order[top - 1] - order[top]))
+    return ids.tolist(), (s[ids] * float(router["scale"])).tolist(), margin
 
 
-def mixture_of_experts(h: torch.Tensor, W: dict, mlp: dict) -> torch.Tensor:
+def mixture_of_experts(h: torch.Tensor, W: dict, mlp: dict, margins: list | None = None) -> torch.Tensor:
+    """``margins`` (a list) receives, per token, how close the router's call was."""
     T = h.shape[0]
     router = mlp["router"]
     z = h @ W["router"].T
     out = torch.zeros_like(h)
     for t in range(T):
-        ids, weights = choose_experts(z[t], W["correction"], router)
+        ids, weights, margin = choose_experts(z[t], W["correction"], router)
+        if margins is not None:
+            margins.append(margin)
         for e, w in zip(ids, weights):
             out[t] = out[t] + w * gated_unit(h[t:t + 1], W, f"e{e}.")[0]
     if mlp.get("shared"):
@@ -251,9 +262,10 @@ def part(state: dict, prefix: str) -> dict:
     return {k[len(prefix):]: v for k, v in state.items() if k.startswith(prefix)}
 
 
-def ruburax_logits(state: dict, cfg: dict, tokens, dtype=torch.float64, streams: list | None = None) -> torch.Tensor:
+def ruburax_logits(state: dict, cfg: dict, tokens, dtype=torch.float64, streams: list | None = None,
+                   margins: list | None = None) -> torch.Tensor:
     """Logits ``[T, vocab]`` of one sequence from position 0.  ``streams`` (a list) receives the residual
-    stream after every layer."""
+    stream after every layer, ``margins`` (a list) the routers' closest calls, layer by layer, token by token."""
     st = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in state.items()}
     eps, mult = float(cfg["norm"]["eps"]), float(cfg["residual_mult"])
     T = len(tokens)
@@ -278,7 +290,7 @@ def ruburax_logits(state: dict, cfg: dict, tokens, dtype=torch.float64, streams:
         mlp = layer.get("mlp")
         if mlp is not None:
             W = part(st, p + "mlp.")
-            f = gated_unit(x, W) if mlp["kind"] == "dense" else mixture_of_experts(x, W, mlp)
+            f = gated_unit(x, W) if mlp["kind"] == "dense" else mixture_of_experts(x, W, mlp, margins)
             x = x + mult * rms_norm(f, st[p + "norm2"], eps)
         side = cfg.get("token_side")
         if side:

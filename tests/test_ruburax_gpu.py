@@ -1,0 +1,616 @@
+"""The Ruburax architecture in the engine against the plain implementation (``plain_ruburax``):
+every mechanism alone at the kernel level, then whole models of three small configurations
+under every way of cutting the work, in float32 and bfloat16, long decoding, and greedy generation
+through the scheduler.  Weights and inputs are made so that a fault shows: a key that stands out
+hundreds of tokens back and at a page's border, a sink that takes half of the weight, a memory whose
+first token must still be readable after hundreds of forgetful ones, states that must be zeroed when a
+slot is used again, caches filled with NaN where nothing was written."""
+
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ruburax as P
+import trace_util as T
+from ruburax_configs import CONFIGS, PAGE_SIZE, attention, attn, config, prompt, random_state, rot
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+LENGTHS = {"A": [3, 19, 64, 90, 41], "B": [1, 2, 37, 70], "C": [50, 5, 33, 81]}
+# A choice score this close to the first one left out is a close call (bfloat16 activations move a
+# router logit by about 0.01): the other expert is as good an answer, and through keys, values and states
+# it reaches the tokens behind: in float32 a request is compared up to its first close call, in bfloat16,
+# where close calls are many, every row whose own routing is none.
+CLOSE_CALL = {"float32": 2e-4, "bfloat16": 0.02}
+MIN_CHECKED = {"float32": 0.5, "bfloat16": 0.5}
+
+
+def ops():
+    from mini_infer_b200.csrc import ops as o
+    return o
+
+
+def requests_for(which):
+    return {f"r{i}": prompt(CONFIGS[which], n, salt=i) for i, n in enumerate(LENGTHS[which])}
+
+
+_plain_cache = {}
+
+
+def plain_with_margins(state, cfg, toks):
+    m = []
+    logits = P.ruburax_logits(state, cfg, toks, torch.float64, margins=m).numpy()
+    n_moe = sum(1 for l in cfg["layers"] if l.get("mlp") and l["mlp"]["kind"] == "moe")
+    margin = np.array(m).reshape(n_moe, len(toks)).min(axis=0) if n_moe else np.full(len(toks), np.inf)
+    return logits, margin
+
+
+def plain_for(which):
+    """float64 logits of every request, and per request and position its closest router call."""
+    if which not in _plain_cache:
+        cfg = CONFIGS[which]
+        state = random_state(cfg, seed=11)
+        logits, margins = {}, {}
+        for rid, toks in requests_for(which).items():
+            logits[rid], margins[rid] = plain_with_margins(state, cfg, toks)
+        _plain_cache[which] = (state, logits, margins)
+    return _plain_cache[which]
+
+
+def poisoned(runner):
+    for st in runner.cache.storage:
+        st.fill_(float("nan"))            # a slot that was never written must never be read
+    for arena in runner.cache.state_arenas.values():
+        arena.fill_(float("nan"))         # a state must be zeroed when its slot is handed out
+    return runner
+
+
+def make_runner(which, dtype, steps=None, num_blocks=None, max_requests=4, cuda_graph=False):
+    from mini_infer_b200.engine import ModelRunner
+
+    state, _, _ = plain_for(which)
+    ps = PAGE_SIZE[which]
+    if num_blocks is None:
+        num_blocks = T.max_tokens_needed(steps) // ps
+    return poisoned(ModelRunner.from_state_dict(CONFIGS[which], state, dtype=dtype, block_size=ps,
+                                                num_blocks=num_blocks, max_requests=max_requests,
+                                                cuda_graph=cuda_graph))
+
+
+def compare(which, dtype, got):
+    _, want, margins = plain_for(which)
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    tol = T.tolerance(dtype, scale)
+    checked = total = over = far_over = 0
+    for rid, w in want.items():
+        assert got[rid].shape == w.shape
+        close = margins[rid] < CLOSE_CALL[dtype]
+        total += len(w)
+        assert np.isfinite(got[rid]).all(), f"{rid}: non-finite logits"
+        if dtype == "bfloat16":
+            # Every row whose own routing is no close call is compared.  Another choice at an earlier token
+            # reaches a later one through keys, values and states, but weakly; and a head whose few channels
+            # nearly cancel is divided by a small root mean square.  Such rows are few; a wrong key, page or
+            # state moves most rows by tens of percent.
+            keep = np.nonzero(~close)[0]
+            checked += len(keep)
+            err = np.abs(got[rid][keep] - w[keep]).max(axis=1)
+            over += int((err > float(tol)).sum())
+            far_over += int((err > 4 * float(tol)).sum())
+            continue
+        keep = np.arange(int(np.nonzero(close)[0][0]) if close.any() else len(w))
+        checked += len(keep)
+        bad = T.first_bad(got[rid][keep], w[keep], tol)
+        assert bad is None, f"{which} {dtype} {rid}: position {keep[bad]} differs by " \
+                            f"{np.abs(got[rid][keep[bad]] - w[keep[bad]]).max():.3g} (bound {float(tol):.3g})"
+    assert over <= max(2, 0.04 * checked), f"{over} of {checked} rows are over the bound"
+    assert far_over <= max(2, 0.02 * checked), f"{far_over} of {checked} rows are far over the bound"
+    assert checked >= MIN_CHECKED[dtype] * total, f"only {checked} of {total} rows were compared"
+
+
+CUTTINGS = {"whole": T.cut_whole, "last_decoded": T.cut_last_decoded, "portions": T.cut_portions,
+            "mixed": T.cut_mixed}
+
+
+@pytest.mark.parametrize("cutting", list(CUTTINGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_engine_matches_plain_under_every_cutting(which, dtype, cutting):
+    """Whole prompts, prefill then token-by-token decoding, portions down to two tokens, and mixed
+    batches of unequal requests in which slots and pages are freed and used again."""
+    requests = requests_for(which)
+    steps = CUTTINGS[cutting](requests)
+    runner = make_runner(which, dtype, steps)
+    got = T.collect(steps, T.replay_in_process(runner, steps), CONFIGS[which]["vocab"])
+    runner.cache.check()
+    assert runner.cache.num_requests == 0
+    for gi, pool in enumerate(runner.cache.pools):
+        assert runner.cache.num_free_pages(gi) == pool.num_pages
+    compare(which, dtype, got)
+
+
+@pytest.mark.parametrize("which", ["A", "B", "C"])
+def test_float32_logits_do_not_depend_on_the_cutting(which):
+    """In float32 every sum runs in an order that depends on the position alone: the logits of a
+    position are the same bits whole, in portions, decoded, or beside other requests."""
+    requests = requests_for(which)
+    results = {}
+    for name, cut in CUTTINGS.items():
+        steps = cut(requests)
+        runner = make_runner(which, "float32", steps)
+        results[name] = T.collect(steps, T.replay_in_process(runner, steps), CONFIGS[which]["vocab"])
+    for name in ("last_decoded", "portions", "mixed"):
+        for rid in requests:
+            assert np.array_equal(results[name][rid], results["whole"][rid]), f"{which} {name} {rid}"
+
+
+@pytest.mark.parametrize("which,n_pages,salt", [("A", 26, 78), ("C", 14, 77)])
+def test_long_decoding_and_captured_steps(which, n_pages, salt):
+    """One short prompt, then 180 tokens one by one, kernel by kernel and as captured graphs."""
+    from mini_infer_b200.engine import StepEntry
+
+    cfg = CONFIGS[which]
+    state, _, _ = plain_for(which)
+    toks = prompt(cfg, 186, salt=salt)        # prompts whose routers make no close call early on
+    want, margin = plain_with_margins(state, cfg, toks)
+    close = np.nonzero(margin < CLOSE_CALL["float32"])[0]
+    upto = int(close[0]) if close.size else len(toks)
+    assert upto > 60
+    tol = T.tolerance("float32", float(np.abs(want).max()))
+    results = []
+    for graph in (False, True):
+        runner = make_runner(which, "float32", num_blocks=n_pages, cuda_graph=graph)
+        runner.add_request("a")
+        rows = [runner.step([StepEntry("a", toks[:6], list(range(6)))]).logits.cpu().numpy()]
+        for t in toks[6:]:
+            rows.append(runner.step([StepEntry("a", [t], [0])]).logits.cpu().numpy())
+        got = np.concatenate(rows)
+        assert T.first_bad(got[:upto], want[:upto], tol) is None
+        runner.free_request("a")
+        runner.cache.check()
+        results.append(got)
+    assert np.array_equal(results[0], results[1])        # a captured step computes what the step itself does
+
+
+def test_greedy_generation_through_the_scheduler():
+    """Greedy tokens from the engine's own entry point (scheduler, sampler, cache) equal the plain
+    implementation's, fed its own tokens, for several prompts generated together."""
+    from mini_infer_b200.engine import ContinuousScheduler, Request
+    from mini_infer_b200.sampling import SamplingParams
+
+    which = "A"
+    cfg = CONFIGS[which]
+    state, _, _ = plain_for(which)
+    prompts = [prompt(cfg, n, salt=200 + i) for i, n in enumerate([4, 21, 9])]
+    n_new = 12
+    runner = make_runner(which, "float32", num_blocks=32)
+    sched = ContinuousScheduler(runner, max_concurrent=3, max_tokens_per_step=16)
+    results = sched.generate([Request(prompt=p, sampling_params=SamplingParams(), max_tokens=n_new) for p in prompts])
+    sched.stop()
+    for p, r in zip(prompts, results):
+        assert len(r.tokens) == n_new
+        seq = list(p)
+        for tok in r.tokens:
+            logits = P.ruburax_logits(state, cfg, seq, torch.float64)[-1]
+            top2 = torch.topk(logits, 2).values
+            if float(top2[0] - top2[1]) > 1e-3:     # the plain choice is not a close call
+                assert tok == int(logits.argmax()), f"after {len(seq)} tokens"
+            seq.append(tok)
+    runner.cache.check()
+    assert runner.cache.num_requests == 0
+
+
+def test_generation_from_a_model_folder(tmp_path):
+    """A folder with config.json and model.safetensors through ``generate_ids``, the call behind the command line."""
+    import json
+
+    from mini_infer_b200.engine.api import generate_ids
+    from mini_infer_b200.weights.safetensors_io import write_safetensors
+
+    cfg = CONFIGS["B"]
+    state = random_state(cfg, seed=11)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(tmp_path / "model.safetensors"), state)
+    p = prompt(cfg, 11, salt=300)
+    got = generate_ids(str(tmp_path), [p], max_tokens=5, dtype="float32", device=DEV)[0]
+    seq = list(p)
+    for tok in got:
+        logits = P.ruburax_logits(state, cfg, seq, torch.float64)[-1]
+        top2 = torch.topk(logits, 2).values
+        if float(top2[0] - top2[1]) > 1e-3:
+            assert tok == int(logits.argmax())
+        seq.append(tok)
+
+
+def test_first_tokens_of_a_sequence_and_slots_used_again():
+    """A request's first tokens (alone, as a pair, as a longer prompt) start from zero state, a running
+    maximum of zero and empty convolution tails whatever the slot held before: the same prompt gives the
+    same logits in a fresh runner and in slots that other requests have just left."""
+    from mini_infer_b200.engine import StepEntry
+
+    which = "C"
+    cfg = CONFIGS[which]
+    toks = prompt(cfg, 40, salt=5)
+    other = prompt(cfg, 55, salt=6)
+    fresh = make_runner(which, "float32", num_blocks=16)
+    fresh.add_request("x")
+    want = fresh.step([StepEntry("x", toks, list(range(len(toks))))]).logits.cpu().numpy()
+    state, _, _ = plain_for(which)
+    plain, margin = plain_with_margins(state, cfg, toks)
+    upto = int(np.nonzero(margin < CLOSE_CALL["float32"])[0][0]) if (margin < CLOSE_CALL["float32"]).any() else 40
+    assert upto >= 3
+    assert T.first_bad(want[:upto], plain[:upto], T.tolerance("float32", float(np.abs(plain).max()))) is None
+    runner = make_runner(which, "float32", num_blocks=16, max_requests=2)
+    for first in (1, 2, 17):
+        for rid in ("p", "q"):                               # fill both slots and leave them
+            runner.add_request(rid)
+            runner.step([StepEntry(rid, other, [])])
+        runner.free_request("q")
+        runner.free_request("p")
+        runner.add_request("a")
+        rows = [runner.step([StepEntry("a", toks[:first], list(range(first)))]).logits.cpu().numpy(),
+                runner.step([StepEntry("a", toks[first:], list(range(len(toks) - first)))]).logits.cpu().numpy()]
+        runner.free_request("a")
+        assert np.array_equal(np.concatenate(rows), want), f"first portion of {first}"
+    runner.cache.check()
+
+
+# ----------------------------------------------------------------------------- mechanisms alone
+
+
+def rnd(*shape, seed, scale=1.0, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def ctx_for(q_lens, slots):
+    """The part of a step context the state kernels read."""
+    starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+    i32 = lambda a: torch.tensor(np.asarray(a, dtype=np.int32), device=DEV)
+    return SimpleNamespace(q_start=i32(starts), q_len=i32(q_lens), state_slot=i32(slots), n_requests=len(q_lens),
+                           n_tokens=int(sum(q_lens)), decode_only=all(n == 1 for n in q_lens),
+                           host_q_len=list(q_lens))
+
+
+@pytest.mark.parametrize("H,mult,dtype,bound", [(48, 0.7, torch.float32, 3e-6), (40, 1.0, torch.bfloat16, 1e-2),
+                                                (1000, 0.25, torch.bfloat16, 1e-2), (7, 2.0, torch.float32, 3e-6)])
+def test_a_norm_behind_its_branch_adds_to_the_stream(H, mult, dtype, bound):
+    """``stream += mult * w * y * rsqrt(mean(y^2) + eps)`` in fp32 and in place, with the stream's copy in
+    the compute dtype; without a branch, the copy alone."""
+    M, eps = 13, 1e-5
+    stream = rnd(M, H, seed=1, scale=3.0)
+    y = rnd(M, H, seed=2, scale=0.01).to(dtype)              # small rows: the epsilon counts
+    gain = rnd(H, seed=3, scale=0.3) + 1
+    dev = stream.to(DEV).clone()
+    copy = ops().scaled_norm_add(dev, y.to(DEV), gain.to(DEV), eps, mult, dtype)
+    want = stream.double() + mult * P.rms_norm(y.double(), gain.double(), eps)
+    assert (dev.cpu().double() - want).abs().max() <= 3e-6 * want.abs().max()
+    assert copy.dtype == dtype
+    assert (copy.float().cpu().double() - want).abs().max() <= bound * want.abs().max()
+    if dtype == torch.float32:
+        assert copy.data_ptr() == dev.data_ptr()             # the float32 stream is its own copy
+    else:
+        again = ops().scaled_norm_add(dev, None, None, 0.0, 1.0, dtype)
+        assert torch.equal(again, copy)
+
+
+@pytest.mark.parametrize("dim,index,layers,dtype,bound", [(6, 2, 4, torch.float32, 2e-5), (3, 0, 6, torch.float32, 2e-5),
+                                                          (16, 7, 8, torch.bfloat16, 2e-2), (5, 1, 2, torch.bfloat16, 2e-2)])
+def test_token_side_input(dim, index, layers, dtype, bound):
+    """A layer's columns of the token's row of the side table, gated by ``gelu_tanh(W_gate x)``, projected,
+    normed and added; the part keeps its own columns only."""
+    from mini_infer_b200.parts import PartSpec, build_part
+    from mini_infer_b200.parts.base import StreamCopy
+
+    M, H, V, eps, mult = 9, 40, 17, 1e-5, 0.6
+    W = {"gate": rnd(dim, H, seed=5, scale=0.4).to(dtype), "proj": rnd(H, dim, seed=6).to(dtype),
+         "norm": rnd(H, seed=7, scale=0.2) + 1}
+    table = rnd(V, layers * dim, seed=8).to(dtype)
+    ids = [3, 0, 16, 3, 9, 9, 1, 2, 15]
+    part = build_part("stream", PartSpec("token_side_input", {"hidden_size": H, "vocab_size": V, "dim": dim, "index": index,
+                                                             "table_width": layers * dim, "eps": eps, "mult": mult}))
+    part.bind({"table": table.to(DEV), "gate": W["gate"].to(DEV), "proj": W["proj"].to(DEV), "norm": W["norm"].to(DEV)},
+              dtype, torch.device(DEV))
+    assert part.table.shape == (V, dim)
+    stream = rnd(M, H, seed=9, scale=2.0)
+    x = stream.to(dtype)                                       # what the branches read: the stream's copy
+    dev = stream.to(DEV).clone()
+    ctx = SimpleNamespace(token_ids=torch.tensor(ids, dtype=torch.int32, device=DEV))
+    out, res = part.forward(StreamCopy.of(x.to(DEV)), dev, ctx, None)
+    assert res is dev and isinstance(out, StreamCopy)
+    W64 = {k: v.double() for k, v in W.items()}
+    want = stream.double() + mult * P.token_side_input(x.double(), W64, table.double(), ids, index, dim, eps)
+    assert (dev.cpu().double() - want).abs().max() <= bound * want.abs().max()
+    assert (out.rounded.float().cpu().double() - want).abs().max() <= max(bound, 1e-2 if dtype == torch.bfloat16 else 0) * want.abs().max()
+
+
+@pytest.mark.parametrize("d,dv,rdims,scaling", [(24, 16, 12, (4.0, 2.0, 6.0, 40)), (48, 48, 48, (8.0, 1.0, 4.0, 512)),
+                                                (10, 14, 10, None), (7, 3, 2, (2.0, 0.5, 3.0, 16)), (20, 28, 0, None)])
+def test_biases_head_norm_and_rescaled_rotation(d, dv, rdims, scaling):
+    """Biases on q, k and v, then the RMS norm over the head with a shared gain, then the rotation whose
+    long waves are slowed down, in place, against the plain functions, at positions from 0 to a million; a layer
+    without keys of its own prepares its queries alone."""
+    from mini_infer_b200.parts import PartSpec, build_part
+
+    M, nq, nkv = 9, 4, 2
+    width = nq * d + nkv * d + nkv * dv + 5          # some columns behind, which must stay untouched
+    packed = rnd(M, width, seed=8)
+    pos = [0, 1, 2, 3, 100, 101, 4095, 1000000, 8]
+    base, eps = 300.0, 1e-5
+    qg, kg = rnd(d, seed=9) + 1, rnd(d, seed=10) + 1
+    bias = rnd(width - 5, seed=12, scale=0.5)
+    r = rot(rdims, base, scaling) if rdims else None
+    freq = None
+    if rdims:
+        sc = None
+        if scaling:
+            sc = {"factor": scaling[0], "low_freq_factor": scaling[1], "high_freq_factor": scaling[2],
+                  "original_max_position_embeddings": scaling[3]}
+        position = build_part("position", PartSpec("rotary", {"head_dim": d, "theta": base, "rotary_dim": rdims,
+                                                               "span": "rotated", "scaling": sc}))
+        position.bind({}, torch.float32, torch.device(DEV))
+        freq = position.freq64
+        assert (freq.cpu() - torch.tensor(P.rotation_frequencies(r), dtype=torch.float64)).abs().max() <= 1e-15
+        if scaling:                                  # all three bands are there
+            plain = torch.tensor([base ** (-2.0 * i / rdims) for i in range(rdims // 2)], dtype=torch.float64)
+            ratio = (freq.cpu() / plain)
+            assert ratio.max() == 1.0 and ratio.min() <= 1.0 / scaling[0] + 1e-12 or rdims <= 2
+    dev = packed.to(DEV).clone()
+    args = dict(q_gain=qg.to(DEV), k_gain=kg.to(DEV), eps=eps, rot=rdims,
+                positions=torch.tensor(pos, dtype=torch.int32, device=DEV), freq=freq)
+    ops().qk_norm_rope_store(dev, 0, nq * d, (nq + nkv) * d, nq, nkv, d, dv, bias=bias.to(DEV), **args)
+    got = dev.cpu().double()
+    x = packed.double()
+    xb = x.clone()
+    xb[:, :width - 5] += bias.double()
+    for off, n, gain in ((0, nq, qg), (nq * d, nkv, kg)):
+        heads = P.rms_norm(xb[:, off:off + n * d].reshape(M, n, d), gain.double(), eps)
+        want = P.rotate_half_layout(heads, pos, r).reshape(M, n * d)
+        assert (got[:, off:off + n * d] - want).abs().max() <= 3e-6 * max(1.0, want.abs().max())
+    v0 = (nq + nkv) * d
+    assert (got[:, v0:v0 + nkv * dv] - xb[:, v0:v0 + nkv * dv]).abs().max() <= 1e-6
+    assert torch.equal(got[:, v0 + nkv * dv:], x[:, v0 + nkv * dv:])     # the columns behind are not touched
+    # queries alone
+    dev = packed.to(DEV).clone()
+    ops().qk_norm_rope_store(dev, 0, nq * d, None, nq, 0, d, dv, bias=bias[:nq * d].contiguous().to(DEV), **args)
+    assert torch.equal(dev.cpu()[:, nq * d:], packed[:, nq * d:])
+    assert (dev.cpu().double()[:, :nq * d] - got[:, :nq * d]).abs().max() == 0
+
+
+@pytest.mark.parametrize("heads,dk,dv,cap,dtype,portions", [
+    (2, 12, 36, 5.0, torch.float32, (1, 17, 2, 1, 1, 20, 3)), (1, 64, 32, 15.0, torch.float32, (1, 17, 2, 1, 1, 20, 3)),
+    (3, 9, 5, 3.0, torch.float32, (2, 1, 40, 1)), (6, 32, 48, 15.0, torch.float32, (33, 1, 1, 1)),
+    (2, 24, 40, 15.0, torch.bfloat16, (300, 1, 140, 129)), (1, 128, 64, 8.0, torch.bfloat16, (513,)),   # chunks side by side
+    (2, 16, 8, 20.0, torch.float32, (700, 1, 1, 2))])
+def test_matrix_memory_state_running_maximum_and_a_far_key(heads, dk, dv, cap, dtype, portions):
+    """The matrix, its normaliser and the running maximum through portions and decoded tokens, two slots
+    apart from the one in use, against the plain mixer over the whole sequence.  The first head's forget gates
+    are wide open and its third token's input gate stands far above the others': what the last tokens read is
+    that token's value, hundreds of tokens back, and the running maximum, set by it, is what keeps
+    the later exponentials in range."""
+    Tn, Hd, eps = sum(portions), 16, 1e-5
+    hk, hv = heads * dk, heads * dv
+    W = {"q": rnd(hk, Hd, seed=20, scale=0.4), "k": rnd(hk, Hd, seed=21, scale=0.4), "v": rnd(hv, Hd, seed=22, scale=0.4),
+         "g": rnd(hv, Hd, seed=23, scale=0.4), "o": torch.eye(hv), "norm": rnd(hv, seed=24, scale=0.3) + 1,
+         "i": rnd(heads, Hd, seed=25, scale=0.5), "i.b": rnd(heads, seed=26), "f": rnd(heads, Hd, seed=27, scale=0.5),
+         "f.b": rnd(heads, seed=28) + 2.0}
+    W["f"][0] = 0.0
+    W["f.b"][0] = 30.0                                       # head 0 forgets nothing: log f = -exp(-cap) and less
+    W = {n: w.to(dtype).float() for n, w in W.items()}
+    h = rnd(Tn, Hd, seed=29).to(dtype).float()
+    h[2] = W["i"][0] / W["i"][0].norm() * 4.0                # token 2 opens head 0's input gate wide
+    h = h.to(dtype).float()
+    m = {"heads": heads, "dim": dk, "vdim": dv, "gate_cap": cap}
+    W64 = {n: w.double() for n, w in W.items()}
+    want = P.matrix_memory(h.double(), W64, m, eps)
+    without = h.clone()
+    without[2] = 0.0
+    far = P.matrix_memory(without.double(), W64, m, eps)
+    assert (want[-1, :dv] - far[-1, :dv]).abs().max() > 0.1 * want[-1, :dv].abs().max()      # the far token counts
+    m_off = heads * dk * (dv + 1)
+    state = torch.full((3, m_off + heads), float("nan"), device=DEV)
+    state[1].zero_()
+    w_in = torch.cat([W[n] for n in ("q", "k", "v", "g")]).double()
+    w32 = torch.cat([W["i"], W["f"]]).double()
+    f32 = lambda t: t.float().to(DEV).contiguous()
+    got, t0 = [], 0
+    for n in portions:
+        hp = h[t0:t0 + n].double()
+        proj = (hp @ w_in.T).to(dtype).to(DEV)
+        z = (hp @ w32.T).float().to(DEV)
+        ctx = ctx_for([n], [1])
+        gates = ops().mlstm_gates(z, f32(W["i.b"]), f32(W["f.b"]), cap, heads, state, m_off, ctx)
+        o = ops().gla_scan(proj[:, :hk], proj[:, hk:2 * hk], proj[:, 2 * hk:2 * hk + hv], None, None, 1.0, dk ** -0.5,
+                           heads, dk, dv, state, ctx, tok_gates=gates, extra_col=True)
+        out = torch.empty((n, hv), dtype=dtype, device=DEV)
+        ops().headnorm_gate(o, f32(W["norm"]), proj[:, 2 * hk + hv:], out, heads, dv, eps, "sigmoid", 1.0,
+                            tok_gates=gates, den_eps=1e-6)
+        got.append(out.float().cpu().double())
+        t0 += n
+    got = torch.cat(got)
+    # a head's output is divided by its root mean square: where the read-out nearly cancels, rounding of the
+    # bfloat16 projections moves a row by more; such rows are few
+    bound = (2e-5 if dtype == torch.float32 else 3e-2) * max(1.0, want.abs().max())
+    err = (got - want).abs().max(dim=1).values
+    assert err.max() <= (1 if dtype == torch.float32 else 4) * bound
+    assert (err > bound).sum() <= 0.01 * Tn
+    assert torch.isnan(state[0]).all() and torch.isnan(state[2]).all()      # other slots are never touched
+    assert torch.isfinite(state[1]).all()
+
+
+@pytest.mark.parametrize("E,top,ff,H,M,groups,scale,shared", [
+    (12, 3, 20, 40, 33, (4, 2), 1.5, 24), (10, 2, 24, 48, 70, (5, 1), 2.5, 0), (5, 1, 12, 40, 5, None, 2.0, 8),
+    (4, 4, 16, 36, 9, None, 1.0, 0), (8, 3, 8, 40, 200, (2, 1), 0.7, 16), (9, 2, 10, 36, 7, (3, 3), 1.0, 0),
+    (64, 4, 16, 64, 50, (8, 3), 1.0, 32), (40, 6, 72, 64, 130, (10, 4), 1.0, 0), (8, 4, 96, 192, 40, (4, 3), 2.5, 128)])
+@pytest.mark.parametrize("dtype,bound", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_sigmoid_router_with_correction_groups_and_gated_shared_expert(E, top, ff, H, M, groups, scale, shared, dtype,
+                                                                       bound):
+    """The choice by sigmoid score plus correction within the groups whose two best choice scores sum highest
+    (corrections reach below zero, so an expert that is out must count as minus infinity, not as 0), the
+    weights without the correction and not renormalised, the weighted sum of the experts, and the shared
+    expert under its own sigmoid gate, against the plain token loop."""
+    from mini_infer_b200.parts import PartSpec, build_part
+
+    x = rnd(M, H, seed=60).to(dtype)
+    W = {"router": rnd(E, H, seed=61, scale=0.5).to(dtype), "correction": (rnd(E, seed=62, scale=0.6) - 0.7).to(dtype)}
+    for e in range(E):
+        W[f"e{e}.gate"] = rnd(ff, H, seed=100 + e, scale=0.4).to(dtype)
+        W[f"e{e}.up"] = rnd(ff, H, seed=200 + e, scale=0.4).to(dtype)
+        W[f"e{e}.down"] = rnd(H, ff, seed=300 + e, scale=0.2).to(dtype)
+    router = {"experts": E, "top": top, "scale": scale}
+    if groups:
+        router["groups"] = {"count": groups[0], "keep": groups[1]}
+    mlp = {"kind": "moe", "router": router, "expert": {"ff": ff}}
+    if shared:
+        mlp["shared"] = {"ff": shared}
+        W.update({"shared.gate": rnd(shared, H, seed=63, scale=0.4).to(dtype), "shared.up": rnd(shared, H, seed=64, scale=0.4).to(dtype),
+                  "shared.down": rnd(H, shared, seed=65, scale=0.2).to(dtype), "shared.sg": rnd(1, H, seed=66, scale=0.5).to(dtype)})
+    margins = []
+    W64 = {k: v.double() for k, v in W.items()}
+    want = P.mixture_of_experts(x.double(), W64, mlp, margins)
+    ok = torch.tensor(margins) > (1e-4 if dtype == torch.float32 else 1e-2)
+    assert ok.sum() >= 0.6 * M
+    assert (W64["correction"] < -1.0).any()          # some choice scores are negative
+    dx = x.to(DEV)
+    ids, wts = ops().moe_route(dx, W["router"].to(DEV), top, scores="sigmoid", groups=groups[0] if groups else 0,
+                               keep_groups=groups[1] if groups else 0, scale=scale,
+                               correction=W["correction"].float().to(DEV), group_top2=True)
+    z = x.double() @ W64["router"].T
+    for t in range(M):
+        if not ok[t]:
+            continue
+        idx, w, _ = P.choose_experts(z[t], W64["correction"], router)
+        assert ids[t].cpu().tolist() == idx, f"token {t}"
+        assert (wts[t].cpu().double() - torch.tensor(w)).abs().max() < (1e-5 if dtype == torch.float32 else 1e-2) * scale
+    part = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": H, "experts": E, "top": top, "expert_ff": ff, "activation": "silu", "scores": "sigmoid",
+        "correction": True, "route_scale": scale, "groups": groups[0] if groups else 0,
+        "keep_groups": groups[1] if groups else 0, "group_score": "top2", "shared_ff": shared,
+        "shared_gate": "sigmoid" if shared else None}))
+    part.bind({k: v.to(DEV) for k, v in W.items()}, dtype, torch.device(DEV))
+    out = part.forward(dx, SimpleNamespace())
+    assert (out.float().cpu().double() - want)[ok].abs().max() <= bound * max(1.0, want.abs().max())
+
+
+def attention_runner(n_tokens, page, dtype, sizes, sink, reader=False):
+    """A runner of one attention layer (``sizes``: query heads, key heads, key size, value size), or of two
+    where the second reads the first one's keys and values, whose planner, pages and choice of kernel the
+    kernel-level test borrows."""
+    from mini_infer_b200.engine import ModelRunner
+
+    nq, nkv, d, dv = sizes
+    layers = [attention(attn(nq, nkv, d, dv, 64.0), None)]
+    if reader:
+        layers.append(attention(attn(nq, nkv, d, dv, 64.0, kv_from=0), None))
+    cfg = config(layers, vocab=8, width=16, eps=1e-6, mult=1.0, logit_scale=1.0)
+    state = random_state(cfg, seed=3)
+    for i in range(len(layers)):
+        state[f"l{i}.mix.sink"] = torch.full((nq,), sink, dtype=torch.bfloat16)
+    return poisoned(ModelRunner.from_state_dict(cfg, state, dtype=dtype, block_size=page,
+                                                num_blocks=-(-n_tokens // page) + 1, max_requests=2))
+
+
+# keys and values of two sizes and of one; heads of 48, 64 and 128 in bfloat16 take the tensor-core kernels where they
+# take sinks; with and without shared key heads
+@pytest.mark.parametrize("sizes", [(2, 1, 16, 12), (8, 2, 48, 48), (4, 2, 64, 64), (8, 1, 128, 128), (3, 3, 40, 24)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sinks_page_borders_far_keys_and_another_layers_keys(dtype, sizes):
+    """One key is made to stand out (it points where the queries point, all others across), and the sink is as
+    large as its score: a query behind the key returns half of its value (the sink takes the other half and
+    has no value), a query before it sees ones under a sink that weighs as much as 64 keys would.  The key
+    sits at a page's last and first slot, at the sequence's first position, and hundreds of tokens back; the
+    tokens come as one prompt, in portions, and one by one; a second layer reads the same pages with its own
+    queries and its own sink."""
+    from mini_infer_b200.engine import StepEntry
+
+    nq, nkv, d, dv = sizes
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+
+    def run(n_tokens, marked, page, portions, sink):
+        runner = attention_runner(n_tokens, page, dtype, sizes, sink, reader=True)
+        first, second = runner.model.blocks[0].mixer, runner.model.blocks[1].mixer
+        assert first.own_kv and not second.own_kv and second.in_width == nq * d
+        runner.add_request("a")
+        packed = torch.zeros(n_tokens, (nq + nkv) * d + nkv * dv)
+        packed[:, 0:nq * d:d] = 1.0                          # queries: e0
+        for kh in range(nkv):
+            packed[:, (nq + kh) * d + 1] = 1.0               # keys: e1 ...
+            packed[marked, (nq + kh) * d + 1] = 0.0
+            packed[marked, (nq + kh) * d] = 1.0              # ... the marked key: e0
+        packed[:, (nq + nkv) * d:] = 1.0                     # values: ones, the marked value: tens
+        packed[marked, (nq + nkv) * d:] = 10.0
+        outs, outs2, t0 = [], [], 0
+        for n in portions:
+            ctx, caches, _, _ = runner.stepper.plan([StepEntry("a", [0] * n, [])])
+            runner.stepper.apply_table_updates(ctx)
+            cache, cache2 = caches
+            assert cache2.k.data_ptr() == cache.k.data_ptr() and not cache2.writes
+            dev = packed[t0:t0 + n].to(td).to(DEV)
+            ops().qk_norm_rope_store(dev, 0, nq * d, (nq + nkv) * d, nq, nkv, d, dv,
+                                     slots=ctx.groups[cache.group].slots, kcache=cache.k, vcache=cache.v)
+            out = torch.empty(n, nq * dv, dtype=td, device=DEV)
+            first._attend(dev[:, :nq * d].contiguous(), out, cache, ctx)
+            outs.append(out.float().cpu())
+            out2 = torch.empty(n, nq * dv, dtype=td, device=DEV)
+            second.sinks = torch.full((nq,), -30.0, device=DEV)          # the reader's sink weighs nothing
+            second._attend(dev[:, :nq * d].contiguous(), out2, cache2, ctx)
+            outs2.append(out2.float().cpu())
+            t0 += n
+        assert t0 == n_tokens
+        return torch.cat(outs), torch.cat(outs2)
+
+    def cuttings(n):
+        yield [n]
+        yield [1] * n
+        sizes_, rest = [], n
+        for s in (5, 2, 13, 1, 3, 29, 2, 17, 7) * 10:
+            if rest <= 0:
+                break
+            sizes_.append(min(s, rest))
+            rest -= sizes_[-1]
+        yield sizes_
+
+    tol = 1e-3 if dtype == "float32" else 6e-2
+    for page, marked in ((8, 15), (8, 16), (16, 31), (4, 13), (8, 0), (16, 39)):
+        for portions in cuttings(70):
+            out, out2 = run(70, marked, page, portions, 64.0)
+            for i in range(70):
+                if i < marked:
+                    # scores are all 0 and the sink is 64: the sink takes nearly all of the weight
+                    assert out[i].abs().max() < 1e-3, (page, marked, i)
+                else:
+                    # behind the key: the key's weight and the sink's are equal, the others' vanish
+                    assert torch.allclose(out[i], torch.full_like(out[i], 5.0), atol=tol * 10), (page, marked, i, portions[:4])
+                want2 = 10.0 if i >= marked else 1.0
+                assert torch.allclose(out2[i], torch.full_like(out2[i], want2), atol=tol * 10), (page, marked, i, portions[:4])
+    for portions in ([700], [690] + [1] * 10):               # a key 696 tokens back
+        out, out2 = run(700, 3, 16, portions, 64.0)
+        assert torch.allclose(out[3:], torch.full_like(out[3:], 5.0), atol=tol * 10)
+        assert torch.allclose(out2[3:], torch.full_like(out2[3:], 10.0), atol=tol * 10)
+        assert torch.allclose(out2[:3], torch.full_like(out2[:3], 1.0), atol=tol * 10)
+
+
+@pytest.mark.parametrize("dtype,bound", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_dense_unit_and_scaled_tied_head(dtype, bound):
+    from mini_infer_b200.parts import PartSpec, build_part
+
+    M, H, I, V = 11, 40, 24, 19
+    x = rnd(M, H, seed=70).to(dtype)
+    W = {"gate": rnd(I, H, seed=71, scale=0.4).to(dtype), "up": rnd(I, H, seed=72, scale=0.4).to(dtype),
+         "down": rnd(H, I, seed=73, scale=0.2).to(dtype)}
+    part = build_part("feed_forward", PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I}))
+    part.bind({"gate_proj.weight": W["gate"].to(DEV), "up_proj.weight": W["up"].to(DEV),
+               "down_proj.weight": W["down"].to(DEV)}, dtype, torch.device(DEV))
+    got = part.forward(x.to(DEV), SimpleNamespace())
+    want = P.gated_unit(x.double(), {k: v.double() for k, v in W.items()})
+    assert (got.float().cpu().double() - want).abs().max() <= bound * max(1.0, want.abs().max())
+    table = rnd(V, H, seed=74).to(dtype)
+    head = build_part("head", PartSpec("linear_head", {"vocab_size": V, "hidden_size": H, "tied": True, "scale": 0.37}))
+    head.bind({}, dtype, torch.device(DEV), tied_weight=table.to(DEV))
+    logits = head.forward(x.to(DEV))
+    assert logits.dtype == torch.float32
+    ref = (x.double() @ table.double().T) * 0.37
+    assert (logits.cpu().double() - ref).abs().max() <= 1e-5 * ref.abs().max()
