@@ -440,6 +440,127 @@ def vepevik_numbers(s: dict, v: dict, layers: int, batch: int, context: float, t
     return nbytes, flops
 
 
+# The Ruburax architecture at the same widths: layers in the order recurrent unit, attention with a sink,
+# attention that reads the keys and values of the layer before it, attention beside a matrix memory; the
+# first layer's feed-forward is dense (Llama's per-token size), the others are experts chosen by sigmoid
+# scores within groups, with a gated shared expert; every layer takes a per-layer input from the token.
+RUBURAX_SIZES = {
+    "2k": dict(groups=8, keep=4, side=64),
+    "4k": dict(groups=8, keep=4, side=128),
+}
+
+
+def ruburax_design(s: dict, u: dict, layers: int) -> dict:
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5,
+                                     "groups": {"count": u["groups"], "keep": u["keep"]}},
+           "expert": {"ff": s["ff"]}, "shared": {"ff": s["shared_ff"]}}
+    dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["shared_ff"]}
+    d = s["dim"]
+    scaled = {"base": 500000.0, "dims": d, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "rot": scaled}
+    unit = {"type": "rglru", "mixer": {"width": s["unit_width"], "blocks": s["blocks"], "conv": s["conv"]}}
+    both = {"type": "parallel",
+            "mixer": {"left": dict(att, rot={"base": 10000.0, "dims": s["rot"]}),
+                      "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"], "gate_cap": 15.0},
+                      "left_scale": 0.6, "right_scale": 0.5}}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind == 0:
+            layer = dict(unit)
+        elif kind == 1:
+            layer = {"type": "attention", "mixer": dict(att)}
+        elif kind == 2:
+            layer = {"type": "attention", "mixer": dict(att, kv_from=i - 1)}
+        else:
+            layer = dict(both)
+        out.append(dict(layer, mlp=dense if i == 0 else moe))
+    return {"architecture": "Ruburax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "residual_mult": 0.5, "logit_scale": 0.5, "token_side": {"dim": u["side"]}, "layers": out}
+
+
+def ruburax_numbers(s: dict, u: dict, layers: int, batch: int, context: float, tokens: int) -> tuple[float, float]:
+    """(bytes a decode step of ``batch`` requests at ``context`` must move, floating-point operations of a
+    prefill of ``tokens``): weights once (of the experts, those the batch's tokens choose in expectation), the
+    cache rows of every attention layer (a layer that reads another's reads them again), the states read and
+    written; products, the causal half of the scores, and two products per token and matrix state."""
+    H, E, top, ff = s["width"], s["experts"], s["top"], s["ff"]
+    heads, nkv, d = s["heads"], s["kv_heads"], s["dim"]
+    C, bw = s["unit_width"], s["unit_width"] // s["blocks"]
+    hk, hv = s["r_heads"] * s["r_dim"], s["r_heads"] * s["r_vdim"]
+    own = H * d * (2 * heads + 2 * nkv)
+    mix_w = {0: 3 * H * C + 2 * C * bw, 1: own, 2: 2 * H * d * heads,
+             3: own + H * (2 * hk + 3 * hv + 2 * s["r_heads"])}
+    hit = E * (1.0 - (1.0 - 1.0 / E) ** (batch * top))
+    dense_w = 3 * H * (top * ff + s["shared_ff"])
+    side_w = 2 * H * u["side"]
+    params_decode = params_token = cache = state = attention = recur = 0.0
+    for i in range(layers):
+        kind = i % 4
+        shared = 3 * H * s["shared_ff"] + H
+        params_decode += mix_w[kind] + side_w + (dense_w if i == 0 else H * E + hit * 3 * H * ff + shared)
+        params_token += mix_w[kind] + side_w + (dense_w if i == 0 else H * E + top * 3 * H * ff + shared)
+        if kind:
+            cache += 2.0 * batch * context * 2 * nkv * d
+            attention += 2.0 * tokens * tokens * heads * d
+        if kind == 0:
+            state += 8.0 * batch * s["conv"] * C
+        if kind == 3:
+            state += 8.0 * batch * s["r_heads"] * s["r_dim"] * (s["r_vdim"] + 1)
+            recur += 4.0 * tokens * s["r_heads"] * s["r_dim"] * (s["r_vdim"] + 1)
+    side_rows = 2.0 * batch * layers * u["side"]
+    nbytes = 2.0 * (params_decode + s["vocab"] * H) + cache + state + side_rows
+    flops = 2.0 * tokens * params_token + 2.0 * s["vocab"] * H + attention + recur
+    return nbytes, flops
+
+
+def run_ruburax_designs(args) -> int:
+    import torch
+
+    from mini_infer_b200.engine import ModelRunner
+
+    peaks = load_peaks()
+    warmup = max(3, args.warmup)
+    out = {"scenario": "designs", "design": "ruburax", "dtype": "bf16", "data": "synthetic", "batch": args.batch,
+           "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks, "sizes": {}}
+    clocks = ClockSampler()
+    clocks.start()
+    for name in args.design_sizes.split(","):
+        s, u = DESIGN_SIZES[name], RUBURAX_SIZES[name]
+        layers = args.layers or 4
+        ruvurax, llama = design_configs(s, layers)
+        cap = args.batch * (args.context + args.steps + warmup + 64) + 2 * PREFILL_TOKENS
+        mid = args.context + warmup + args.steps / 2.0
+        row = {"layers": layers}
+        for label, raw in (("ruburax", ruburax_design(s, u, layers)), ("ruvurax", ruvurax), ("llama", llama)):
+            runner = ModelRunner.from_random(raw, seed=0, gain_std=0.0, device="cuda:0", dtype="bfloat16",
+                                             num_blocks=cap // PAGE + 8, block_size=PAGE, max_requests=args.batch,
+                                             cuda_graph=True)
+            ms, launches = time_decode(runner, args.batch, args.context, args.steps, warmup)
+            pms = time_prefill(runner, PREFILL_TOKENS, repeats=3, warmup=2)
+            if label == "ruburax":
+                nbytes, flops = ruburax_numbers(s, u, layers, args.batch, mid, PREFILL_TOKENS)
+            elif label == "llama":
+                flops = prefill_flops(raw, layers, PREFILL_TOKENS)
+                nbytes = decode_bytes(raw, layers, args.batch, mid)
+            else:
+                nbytes, flops = ruvurax_numbers(s, layers, args.batch, args.context, PREFILL_TOKENS)
+            row[label] = {
+                "decode_tok_s": round(args.batch * 1000.0 / ms, 1), "decode_ms": round(ms, 4),
+                "decode_gbs": round(nbytes / (ms * 1e-3) / 1e9, 1),
+                "decode_frac_of_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pms, 1), "prefill_ms": round(pms, 3),
+                "prefill_frac_of_bf16": round(flops / (pms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+                "launches_per_decode_step": launches // max(1, args.steps),
+            }
+            del runner
+            torch.cuda.empty_cache()
+        out["sizes"][name] = row
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def run_vepevik_designs(args) -> int:
     import torch
 
@@ -1006,9 +1127,9 @@ def main() -> int:
                     help="decode: the contract line; long-mixed: many requests of very different lengths "
                          "through the scheduler (a line of its own); serving: the reference's published "
                          "workload, 1024 tokens in and 128 out, single requests and 16 together (a line of its own); "
-                         "designs: the Ruvurax (or, with --design, the Lilulix or the Vepevik) architecture beside Llama at equal sizes, prefill and decode "
+                         "designs: the Ruvurax (or, with --design, the Lilulix, the Vepevik or the Ruburax) architecture beside Llama at equal sizes, prefill and decode "
                          "(a line of its own)")
-    ap.add_argument("--design", default="ruvurax", choices=["ruvurax", "lilulix", "vepevik"],
+    ap.add_argument("--design", default="ruvurax", choices=["ruvurax", "lilulix", "vepevik", "ruburax"],
                     help="designs: which architecture stands beside Llama")
     ap.add_argument("--design-sizes", default="2k,4k", help="designs: which of the sizes " + ",".join(DESIGN_SIZES))
     ap.add_argument("--requests", type=int, default=64, help="long-mixed: requests started together")
@@ -1040,6 +1161,8 @@ def main() -> int:
         args.layers = None if args.layers == default_layers else args.layers
         if args.design == "vepevik":
             return run_vepevik_designs(args)
+        if args.design == "ruburax":
+            return run_ruburax_designs(args)
         return run_lilulix_designs(args) if args.design == "lilulix" else run_designs(args)
     warmup = max(3, args.warmup)
 
