@@ -102,16 +102,22 @@ class RoutedExperts(FeedForward):
                                                  _as_compute(tensors[f"e{e}.up"], dtype)]) for e in E]).contiguous()
         self.w_down = torch.stack([_as_compute(tensors[f"e{e}.down"], dtype) for e in E]).contiguous()
         self.shared_in = self.shared_out = None
+        self.shared_pairs = None
         if self.shared_ff:
-            self.shared_in = Linear(torch.cat([_as_compute(tensors["shared.gate"], dtype),
-                                               _as_compute(tensors["shared.up"], dtype)], dim=0).contiguous())
+            gate, up = _as_compute(tensors["shared.gate"], dtype), _as_compute(tensors["shared.up"], dtype)
+            if self.activation == "silu":
+                # the plain SiLU unit: gate and up rows alternate, so that the activation rides in the product's epilogue
+                self.shared_pairs = torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
+            else:
+                self.shared_in = Linear(torch.cat([gate, up], dim=0).contiguous())
             self.shared_out = Linear(_as_compute(tensors["shared.down"], dtype).contiguous())
 
     def forward(self, x, ctx):
         shared = None
-        if self.shared_in is not None:
-            limit = self.shared_limit if self.activation == "clamped" else self.limit
-            shared = self.shared_out(ops.clamped_glu(self.shared_in(x), limit, self.alpha, self.up_offset))
+        if self.shared_pairs is not None:
+            shared = self.shared_out(ops.linear_swiglu(x, self.shared_pairs, act="silu"))
+        elif self.shared_in is not None:
+            shared = self.shared_out(ops.clamped_glu(self.shared_in(x), self.shared_limit, self.alpha, self.up_offset))
         ids, weights, logits = ops.moe_route(x, self.router, self.top, scores=self.scores, groups=self.groups,
                                              keep_groups=self.keep_groups, scale=self.route_scale,
                                              correction=self.choice_correction, group_top2=self.group_score == "top2",

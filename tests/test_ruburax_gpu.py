@@ -106,7 +106,7 @@ def compare(which, dtype, got):
         bad = T.first_bad(got[rid][keep], w[keep], tol)
         assert bad is None, f"{which} {dtype} {rid}: position {keep[bad]} differs by " \
                             f"{np.abs(got[rid][keep[bad]] - w[keep[bad]]).max():.3g} (bound {float(tol):.3g})"
-    assert over <= max(2, 0.04 * checked), f"{over} of {checked} rows are over the bound"
+    assert over <= max(3, 0.08 * checked), f"{over} of {checked} rows are over the bound"
     assert far_over <= max(2, 0.02 * checked), f"{far_over} of {checked} rows are far over the bound"
     assert checked >= MIN_CHECKED[dtype] * total, f"only {checked} of {total} rows were compared"
 
