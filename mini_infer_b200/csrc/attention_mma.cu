@@ -684,7 +684,8 @@ __device__ __forceinline__ int balanced_part(long long i, long long i1, const in
 template <int DMAX>
 __device__ __noinline__ void balanced_merge_unit(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                  int unit, int g_first, int g_last, int r, int cgrp, int d,
-                                                 bf16* __restrict__ orow) {
+                                                 bf16* __restrict__ orow, float sink_l2) {
+  // sink_l2: a score (times log2 e) that joins the denominator without a key or a value; minus infinity: none
   const float2* ml = reinterpret_cast<const float2*>(part_ml);
   float mm = -INFINITY, LL = 0.f, acc[DMAX / 16];
 #pragma unroll
@@ -742,6 +743,7 @@ __device__ __noinline__ void balanced_merge_unit(const float* __restrict__ part_
       }
     }
   }
+  if (sink_l2 != -INFINITY && mm != -INFINITY) LL += exp2f(sink_l2 - mm);
   const float inv = LL > 0.f ? 1.f / LL : 0.f;
 #pragma unroll
   for (int c = 0; c < DMAX / 16; ++c)
@@ -758,7 +760,9 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
                                  const int* __restrict__ q_start, const int* __restrict__ kv_len, int B, int nq,
                                  int nkv, int d, float scale, int window, int min_chunks, int unit_cost,
                                  float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                                 int* __restrict__ status, const float* __restrict__ rope_cs, int store_kv) {
+                                 int* __restrict__ status, const float* __restrict__ rope_cs, int store_kv,
+                                 const float* __restrict__ sinks) {
+  // sinks [nq] (optional): per head a score that joins the softmax's denominator with neither key nor value.
   // ROPE (the head size is then DMAX exactly): rope_cs holds per query token [d / 2] sines then
   // [d / 2] cosines of its rotary angles; q arrives un-rotated and is rotated here, in registers; and with store_kv
   // the block that comes to a request's newest chunk first rotates the new key, writes it and
@@ -1107,6 +1111,7 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
     const int head = head0 + r;
     if (r < heads_here) {
       if (whole) {
+        if (sinks && m != -INFINITY) L += exp2f(sinks[head] * LOG2E - m);
         const float inv = L > 0.f ? 1.f / L : 0.f;
         bf16* orow = out + (size_t)tok * out_stride + (size_t)head * d;
         for (int k = cgrp; k < d; k += 16) {
@@ -1143,7 +1148,8 @@ attention_decode_balanced_kernel(const bf16* __restrict__ q, int q_stride, bf16*
         const int g_first = (int)(((start + 1) * G - 1) / W), g_last = (int)(((start + n_b) * G - 1) / W);
         if (r < heads_here)
           balanced_merge_unit<DMAX>(part_o, part_ml, unit, g_first, g_last, r, cgrp, d,
-                                    out + (size_t)tok * out_stride + (size_t)head * d);
+                                    out + (size_t)tok * out_stride + (size_t)head * d,
+                                    sinks ? sinks[head] * LOG2E : -INFINITY);
         if (tid == 0) counters[unit] = 0;   // ready for the next call
       }
     }
@@ -1623,7 +1629,8 @@ extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* o
                                             const int* table_rows, int page_size, const int* q_start,
                                             const int* kv_len, int B, int nq, int nkv, int d, float scale, int window,
                                             int grid, float* part_o, float* part_ml, int* counters,
-                                            const float* rope_cs, int store_kv, cudaStream_t stream) {
+                                            const float* rope_cs, int store_kv, const float* sinks,
+                                            cudaStream_t stream) {
   if (B <= 0) return 0;
   if (rope_cs && ((d != 64 && d != 128 && d != 256) || !mi_aligned(rope_cs, 4)))
     MI_REFUSE("attention: rotating inside the decode kernel needs a head size of 64, 128 or 256, got %d", d);
@@ -1644,7 +1651,7 @@ extern "C" int mi_attention_decode_balanced(const void* q, int q_stride, void* o
     MI_LAUNCH((kern), grid, ROPE ? BAL_THREADS : DEC_THREADS, smem, stream, (const bf16*)q, q_stride,     \
               (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, block_table, bt_stride,   \
               table_rows, page_size, page_shift, q_start, kv_len, B, nq, nkv, d, scale, window, 4,        \
-              g_unit_cost, part_o, part_ml, counters, wait_status_ptr(), rope_cs, store_kv);              \
+              g_unit_cost, part_o, part_ml, counters, wait_status_ptr(), rope_cs, store_kv, sinks);       \
   } while (0)
   if (rope_cs) {
     if (d == 64) MI_DECODE_BAL(64, true);

@@ -178,7 +178,8 @@ def _sig_attention_mma(lib: ctypes.CDLL) -> None:
                                                          ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(c_int)]
     lib.mi_attention_decode_balanced.argtypes = [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+        c_void_p]
     lib.mi_attention_decode_balanced_unit_cost.argtypes = [c_int]
     lib.mi_attention_wait_status.argtypes = [c_int]
     lib.mi_set_status_word.argtypes = [c_void_p]
@@ -251,7 +252,7 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
                                 c_void_p, ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mi_mlstm_gates.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, ll, ll, c_void_p,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.mi_delta_scan.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                   c_int, c_float, c_float, c_void_p, ll, ll, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -756,14 +757,17 @@ def _balanced_workspace(device: torch.device, o_floats: int, ml_floats: int, cou
 
 def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, page_size, q_start, kv_len,
                               n_requests, nq, nkv, head_dim, scale, window=0, table_rows=None,
-                              rope_table: torch.Tensor | None = None, store_kv: bool = True) -> None:
+                              rope_table: torch.Tensor | None = None, store_kv: bool = True,
+                              sinks: torch.Tensor | None = None) -> None:
     """bfloat16 decode attention with the keys of all requests spread evenly over persistent
     blocks, whatever the requests' lengths (attention_decode_balanced_kernel): no plan from the
     host, the blocks read the lengths themselves.  With ``rope_table`` (``rope_table()`` of the
     step's positions) q, k and v come as the projection left them (one row per token: q heads, k
     heads, v heads): the kernel rotates q itself and, with ``store_kv``, rotates the new key and
-    writes it and the new value into their page before it reads them."""
-    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, table_rows, rope_table)
+    writes it and the new value into their page before it reads them.  ``sinks`` (fp32 ``[nq]``): a score per
+    head that joins the softmax's denominator without a key or a value."""
+    _cuda(q, out, kcache, vcache, block_table, q_start, kv_len, table_rows, rope_table, sinks)
+    _opt_f32(sinks, nq, "attention_decode (sinks)")
     if rope_table is not None and (rope_table.dtype != torch.float32 or not rope_table.is_contiguous()
                                    or rope_table.shape[-1] != head_dim):
         raise KernelError("attention_decode: the rotary table must be contiguous fp32 [tokens, head_dim]")
@@ -783,7 +787,7 @@ def attention_decode_balanced(q, q_stride, out, kcache, vcache, block_table, pag
         _ptr(q), int(q_stride), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_table),
         block_table.stride(0), _ptr(table_rows), int(page_size), _ptr(q_start), _ptr(kv_len), int(n_requests), nq, nkv,
         head_dim, float(scale), int(window), int(grid.value), _ptr(part_o), _ptr(part_ml), _ptr(count),
-        _ptr(rope_table), 1 if store_kv else 0, _stream())
+        _ptr(rope_table), 1 if store_kv else 0, _ptr(sinks), _stream())
     _finish(lib, rc, "attention_decode")
 
 
@@ -1568,7 +1572,7 @@ def mlstm_gates(z: torch.Tensor, bias_i: torch.Tensor | None, bias_f: torch.Tens
     lib = _lib("recurrent")
     rc = lib.mi_mlstm_gates(_ptr(z), _ptr(z[:, heads:]), z.stride(0), _ptr(bias_i), _ptr(bias_f), float(cap),
                             _ptr(state), stride, int(m_offset), _ptr(ctx.q_start), _ptr(ctx.q_len),
-                            _ptr(ctx.state_slot), _ptr(gates), ctx.n_requests, heads, _stream())
+                            _ptr(ctx.state_slot), _ptr(gates), ctx.n_requests, heads, _max_q_len(ctx), _stream())
     _finish(lib, rc, "mlstm")
     return gates
 

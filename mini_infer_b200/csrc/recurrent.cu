@@ -512,75 +512,72 @@ extern "C" int mi_gla_scan(const void* q, const void* k, int qk_stride, int qk_d
 }
 
 // ------------------------------------------------------------------------------------------
-// scalar gates of a matrix memory with a running maximum.  One warp per (request, head) walks the
-// portion 32 tokens at a time: the lanes compute the capped log gates of their tokens, lane 0 walks
-// m' = max(f + m, i) through them in the order of the positions (one addition and one maximum per
-// token, whatever the cutting), the lanes turn (m, m') into the decay and the input factor.
+// scalar gates of a matrix memory with a running maximum.  One block per (request, head) takes the
+// portion MLSTM_CHUNK tokens at a time: all threads compute the capped log gates of the chunk's tokens
+// into shared memory, one thread walks m' = max(f + m, i) through them in the order of the positions (one
+// addition and one maximum per token, the same whatever the cutting), all threads turn (m, m') into the
+// decay and the input factor.  A step of single tokens needs one warp per (request, head).
 // state row of a request: m [heads] at m_offset.
 // ------------------------------------------------------------------------------------------
-#define MLSTM_WARPS 4
-__global__ void __launch_bounds__(32 * MLSTM_WARPS)
-mlstm_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, int z_stride,
-                   const float* __restrict__ bi, const float* __restrict__ bf_, float cap,
-                   float* __restrict__ state, long long state_stride, long long m_offset,
-                   const int* __restrict__ q_start, const int* __restrict__ q_len,
-                   const int* __restrict__ state_slot, float* __restrict__ gates, int n_requests, int heads) {
+#define MLSTM_CHUNK 1024
+__global__ void mlstm_gates_kernel(const float* __restrict__ zi, const float* __restrict__ zf, int z_stride,
+                                   const float* __restrict__ bi, const float* __restrict__ bf_, float cap,
+                                   float* __restrict__ state, long long state_stride, long long m_offset,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ state_slot, float* __restrict__ gates, int heads) {
   mi_pdl_enter();
-  __shared__ float sh_i[MLSTM_WARPS][32], sh_f[MLSTM_WARPS][32], sh_m[MLSTM_WARPS][33];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int unit = blockIdx.x * MLSTM_WARPS + warp;
-  if (unit >= n_requests * heads) return;
-  const int req = unit / heads, head = unit - req * heads;
+  __shared__ float sh_i[MLSTM_CHUNK], sh_f[MLSTM_CHUNK], sh_m[MLSTM_CHUNK + 1];
+  const int req = blockIdx.x / heads, head = blockIdx.x - req * heads;
   const int len = q_len[req], row0 = q_start[req];
+  if (len <= 0) return;
   float* mp = state + (size_t)state_slot[req] * state_stride + m_offset + head;
   const float inv_cap = 1.f / cap;
   const float b_i = bi ? bi[head] : 0.f, b_f = bf_ ? bf_[head] : 0.f;
-  float m = *mp;
-  for (int t0 = 0; t0 < len; t0 += 32) {
-    const int n = min(32, len - t0);
-    float gi = 0.f, gf = 0.f;
-    if (lane < n) {
-      const size_t r = (size_t)(row0 + t0 + lane);
-      gi = cap * tanhf((zi[r * z_stride + head] + b_i) * inv_cap);
+  if (threadIdx.x == 0) sh_m[0] = *mp;
+  for (int t0 = 0; t0 < len; t0 += MLSTM_CHUNK) {
+    const int n = min(MLSTM_CHUNK, len - t0);
+    for (int l = threadIdx.x; l < n; l += blockDim.x) {
+      const size_t r = (size_t)(row0 + t0 + l);
+      sh_i[l] = cap * tanhf((zi[r * z_stride + head] + b_i) * inv_cap);
       const float a = cap * tanhf((zf[r * z_stride + head] + b_f) * inv_cap);
-      gf = -mi_softplus(-a);                  // logsigmoid
+      sh_f[l] = -mi_softplus(-a);                  // logsigmoid
     }
-    sh_i[warp][lane] = gi;
-    sh_f[warp][lane] = gf;
-    __syncwarp();
-    if (lane == 0) {
-      float run = m;
-      sh_m[warp][0] = run;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float run = sh_m[0];
 #pragma unroll 8
       for (int l = 0; l < n; ++l) {
-        run = fmaxf(sh_f[warp][l] + run, sh_i[warp][l]);
-        sh_m[warp][l + 1] = run;
+        run = fmaxf(sh_f[l] + run, sh_i[l]);
+        sh_m[l + 1] = run;
       }
     }
-    __syncwarp();
-    if (lane < n) {
-      const float before = sh_m[warp][lane], after = sh_m[warp][lane + 1];
-      float* gp = gates + ((size_t)(row0 + t0 + lane) * heads + head) * 3;
-      gp[0] = expf(gf + before - after);
-      gp[1] = expf(gi - after);
+    __syncthreads();
+    for (int l = threadIdx.x; l < n; l += blockDim.x) {
+      const float before = sh_m[l], after = sh_m[l + 1];
+      float* gp = gates + ((size_t)(row0 + t0 + l) * heads + head) * 3;
+      gp[0] = expf(sh_f[l] + before - after);
+      gp[1] = expf(sh_i[l] - after);
       gp[2] = after;
     }
-    m = sh_m[warp][n];
-    __syncwarp();
+    __syncthreads();
+    if (threadIdx.x == 0) sh_m[0] = sh_m[n];
   }
-  if (lane == 0 && len > 0) *mp = m;
+  __syncthreads();
+  if (threadIdx.x == 0) *mp = sh_m[0];
 }
 
 extern "C" int mi_mlstm_gates(const float* zi, const float* zf, int z_stride, const float* bi, const float* bf_,
                               float cap, float* state, long long state_stride, long long m_offset,
                               const int* q_start, const int* q_len, const int* state_slot, float* gates,
-                              int n_requests, int heads, cudaStream_t stream) {
+                              int n_requests, int heads, int longest, cudaStream_t stream) {
+  // longest: the longest portion of the step (sizes the blocks; any value is correct)
   if (n_requests <= 0 || heads <= 0) return 0;
   if (!(cap > 0.f)) MI_REFUSE("mlstm: the gates' cap must be positive, got %g", (double)cap);
   if (m_offset < 0 || m_offset + heads > state_stride) MI_REFUSE("mlstm: the running maxima lie outside the state row");
-  const int units = n_requests * heads;
-  MI_LAUNCH((mlstm_gates_kernel), (units + MLSTM_WARPS - 1) / MLSTM_WARPS, 32 * MLSTM_WARPS, 0, stream, zi, zf, z_stride,
-            bi, bf_, cap, state, state_stride, m_offset, q_start, q_len, state_slot, gates, n_requests, heads);
+  if ((long long)n_requests * heads > 0x7fffffffLL) MI_REFUSE("mlstm: too many blocks for one launch");
+  const int threads = longest <= 32 ? 32 : (longest <= 256 ? 128 : 512);
+  MI_LAUNCH((mlstm_gates_kernel), n_requests * heads, threads, 0, stream, zi, zf, z_stride, bi, bf_, cap, state,
+            state_stride, m_offset, q_start, q_len, state_slot, gates, heads);
   MI_RETURN_LAUNCH_STATUS();
 }
 

@@ -95,7 +95,11 @@ class RoutedExperts(FeedForward):
         E = range(self.experts)
         self.router = _as_compute(tensors["router"], dtype).contiguous()
         if self.shared_gate:     # the gate's row rides in the router's product: its logit comes out in fp32 beside theirs
-            self.router = torch.cat([self.router, _as_compute(tensors["shared.sg"], dtype).reshape(1, -1)]).contiguous()
+            rows = [self.router, _as_compute(tensors["shared.sg"], dtype).reshape(1, -1)]
+            pad = -(self.experts + 1) % 8      # rows of zeros up to a multiple of 8: the library's aligned products
+            if pad:
+                rows.append(torch.zeros((pad, self.hidden), dtype=self.router.dtype, device=self.router.device))
+            self.router = torch.cat(rows).contiguous()
         self.choice_correction = tensors["correction"].to(torch.float32).contiguous() if self.correction else None
         # per expert its gate rows, then its up rows: one operand for a grouped product, two for the own kernels
         self.w_gate_up = torch.stack([torch.cat([_as_compute(tensors[f"e{e}.gate"], dtype),
@@ -122,7 +126,7 @@ class RoutedExperts(FeedForward):
                                              keep_groups=self.keep_groups, scale=self.route_scale,
                                              correction=self.choice_correction, group_top2=self.group_score == "top2",
                                              experts=self.experts, return_logits=True)
-        gate = logits[:, self.experts:] if self.shared_gate else None
+        gate = logits[:, self.experts:self.experts + 1] if self.shared_gate else None
         return ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, self.limit, self.alpha, shared,
                                up_offset=self.up_offset, shared_gate=gate)
 

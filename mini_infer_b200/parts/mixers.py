@@ -277,10 +277,17 @@ class ChunkAttention(ProjectedMixer):
         """bfloat16 with sizes the tensor-core kernels take and aligned rows: those kernels (the balanced
         decode kernel, tcgen05 or mma.sync for prompt portions; scores and softmax in fp32, as everywhere);
         else the kernel for keys and values of two sizes or the CUDA-core kernel."""
-        if (self.sinks is None and q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0
-                and heads.is_contiguous() and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+        tensor_cores = (q.dtype == torch.bfloat16 and self._tensor_core_sizes() and self.scale > 0
+                        and heads.is_contiguous() and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+        if tensor_cores and self.sinks is None:
             ops.attention(q, q.stride(0), heads, cache, ctx, self.nq, self.nkv, self.d, self.scale,
                           chunk=self.chunk or 0)
+        elif tensor_cores and ctx.decode_only and not self.chunk:
+            # single tokens with sinks: the balanced decode kernel, the sink joining the last merge
+            group = ctx.groups[cache.group]
+            ops.attention_decode_balanced(q, q.stride(0), heads, cache.k, cache.v, group.block_table, group.page_size,
+                                          ctx.q_start, ctx.kv_len, ctx.n_requests, self.nq, self.nkv, self.d, self.scale,
+                                          0, table_rows=group.table_rows, sinks=self.sinks)
         else:
             ops.attention_ext(q, heads, cache, ctx, self.nq, self.nkv, self.d, self.dv, self.scale,
                               chunk=self.chunk or 0, sinks=self.sinks)
