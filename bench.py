@@ -451,18 +451,18 @@ RUBURAX_SIZES = {
 
 
 def ruburax_design(s: dict, u: dict, layers: int) -> dict:
-    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 2.5,
+    moe = {"kind": "moe", "router": {"experts": s["experts"], "top": s["top"], "scale": 2.0,
                                      "groups": {"count": u["groups"], "keep": u["keep"]}},
            "expert": {"ff": s["ff"]}, "shared": {"ff": s["shared_ff"]}}
     dense = {"kind": "dense", "ff": s["top"] * s["ff"] + s["shared_ff"]}
     d = s["dim"]
-    scaled = {"base": 500000.0, "dims": d, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    scaled = {"base": 1000000.0, "dims": d, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}
     att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d, "scale": d ** -0.5, "rot": scaled}
     unit = {"type": "rglru", "mixer": {"width": s["unit_width"], "blocks": s["blocks"], "conv": s["conv"]}}
     both = {"type": "parallel",
             "mixer": {"left": dict(att, rot={"base": 10000.0, "dims": s["rot"]}),
-                      "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"], "gate_cap": 15.0},
-                      "left_scale": 0.6, "right_scale": 0.5}}
+                      "right": {"heads": s["r_heads"], "dim": s["r_dim"], "vdim": s["r_vdim"], "gate_cap": 10.0},
+                      "left_scale": 0.7, "right_scale": 0.7}}
     out = []
     for i in range(layers):
         kind = i % 4
@@ -476,7 +476,7 @@ def ruburax_design(s: dict, u: dict, layers: int) -> dict:
             layer = dict(both)
         out.append(dict(layer, mlp=dense if i == 0 else moe))
     return {"architecture": "Ruburax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
-            "residual_mult": 0.5, "logit_scale": 0.5, "token_side": {"dim": u["side"]}, "layers": out}
+            "residual_mult": 0.7, "logit_scale": 0.8, "token_side": {"dim": u["side"]}, "layers": out}
 
 
 def ruburax_numbers(s: dict, u: dict, layers: int, batch: int, context: float, tokens: int) -> tuple[float, float]:

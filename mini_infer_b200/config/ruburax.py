@@ -116,10 +116,12 @@ class RuburaxConfig:
             m = layer.mixer
             if isinstance(m, AttentionConfig) and m.kv_from is not None:
                 j = m.kv_from
-                if not 0 <= j < i or not isinstance(parsed[j].mixer, AttentionConfig) or parsed[j].mixer.kv_from is not None:
-                    raise ConfigError(f"config.json: layers[{i}].mixer.kv_from={j} must name an earlier attention "
-                                      "layer with keys and values of its own")
-                o = parsed[j].mixer
+                o = parsed[j].mixer if 0 <= j < i else None
+                if isinstance(o, ParallelMixerConfig):
+                    o = o.left                  # a parallel layer's keys and values are its attention's
+                if not isinstance(o, AttentionConfig) or o.kv_from is not None:
+                    raise ConfigError(f"config.json: layers[{i}].mixer.kv_from={j} must name an earlier layer with "
+                                      "an attention that has keys and values of its own")
                 if (o.kv_heads, o.dim, o.vdim) != (m.kv_heads, m.dim, m.vdim):
                     raise ConfigError(f"config.json: layers[{i}] reads layer {j}'s keys and values, whose sizes differ")
         return cls(

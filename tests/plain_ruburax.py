@@ -281,7 +281,7 @@ def ruburax_logits(state: dict, cfg: dict, tokens, dtype=torch.float64, streams:
             other = kept[int(m["kv_from"])] if m.get("kv_from") is not None else None
             mixed, kept[i] = softmax_attention(x, W, positions, m, eps, biased=True, sink=True, keys_values=other)
         elif layer["type"] == "parallel":
-            left, _ = softmax_attention(x, part(W, "left."), positions, m["left"], eps, biased=False, sink=False)
+            left, kept[i] = softmax_attention(x, part(W, "left."), positions, m["left"], eps, biased=False, sink=False)
             right = matrix_memory(x, part(W, "right."), m["right"], eps)
             mixed = float(m["left_scale"]) * left + float(m["right_scale"]) * right
         else:

@@ -74,12 +74,13 @@ CONFIGS = {
                  attention(attn(4, 2, 24, 16, 0.3, rot(12, 1000.0, (4.0, 2.0, 6.0, 40)), kv_from=1), experts(6, 2, 16, 2.5)),
                  parallel(attn(6, 3, 16, 8, 0.25, rot(16, 50.0)), (3, 12, 20, 5.0), (0.6, 0.8), experts(9, 4, 12, 0.7, (3, 2), 8))],
                 vocab=59, width=48, eps=1e-5, mult=0.7, logit_scale=1.3, side=6),
-    # no per-layer token input; a parallel layer first; layers without a feed-forward; heads that share nothing;
-    # no rotation in one attention; factors of 1
+    # no per-layer token input; a parallel layer first, whose attention's keys and values the last layer reads;
+    # layers without a feed-forward; heads that share nothing; no rotation in one attention; factors of 1
     "B": config([parallel(attn(2, 2, 10, 14, 0.4), (1, 32, 8, 20.0), (1.0, 0.5), None),
                  attention(attn(3, 1, 16, 16, 0.25, rot(4, 30.0)), experts(5, 1, 12, 2.0)),
                  rglru(24, 1, 1, experts(8, 8, 8, 1.0, (2, 2), 16)),
-                 attention(attn(2, 2, 20, 12, 0.2), None)],
+                 attention(attn(2, 2, 20, 12, 0.2), None),
+                 attention(attn(2, 2, 10, 14, 0.35, kv_from=0), dense(28))],
                 vocab=53, width=40, eps=1e-6, mult=1.0, logit_scale=1.0),
     # odd sizes; an attention that reads keys and values across three other layers; five taps; a cap of 3
     "C": config([attention(attn(6, 3, 12, 9, 0.29, rot(12, 300.0, (8.0, 1.0, 4.0, 64))), dense(36)),
