@@ -544,11 +544,34 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ zi, const float* __
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+      // eight tokens' gates into registers, then their eight dependent steps: the loads stay off the chain
+      // (a token behind the chunk's end has f = 0, i = -inf and leaves the maximum as it is)
       float run = sh_m[0];
-#pragma unroll 8
-      for (int l = 0; l < n; ++l) {
-        run = fmaxf(sh_f[l] + run, sh_i[l]);
-        sh_m[l + 1] = run;
+      float f8[8], i8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        f8[j] = j < n ? sh_f[j] : 0.f;
+        i8[j] = j < n ? sh_i[j] : -INFINITY;
+      }
+      for (int l = 0; l < n; l += 8) {
+        float fn[8], in[8], m8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int k = l + 8 + j;
+          fn[j] = k < n ? sh_f[k] : 0.f;
+          in[j] = k < n ? sh_i[k] : -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          run = fmaxf(f8[j] + run, i8[j]);
+          m8[j] = run;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (l + j < n) sh_m[l + j + 1] = m8[j];
+          f8[j] = fn[j];
+          i8[j] = in[j];
+        }
       }
     }
     __syncthreads();

@@ -4,6 +4,8 @@
     python -m mini_infer_b200.microbench attention_prefill --tokens 2048 [--impl mma]
     python -m mini_infer_b200.microbench gemm_tma --rows 8 --n 28672 --k 4096 [--epilogue stream|stats]
     python -m mini_infer_b200.microbench add_rmsnorm --rows 8 --width 4096
+    python -m mini_infer_b200.microbench norm_add --rows 16384 --width 2048
+    python -m mini_infer_b200.microbench mlstm_gates --rows 2048 --heads 4
     python -m mini_infer_b200.microbench rope_write --rows 2048
     python -m mini_infer_b200.microbench silu_mul --rows 2048 --width 14336
     python -m mini_infer_b200.microbench sample --rows 8 --vocab 128256
@@ -208,6 +210,39 @@ def add_rmsnorm(args, ops, device, flush) -> tuple[float, str]:
     return us, f"{nbytes / us / 1e6:.2f} TB/s"
 
 
+def norm_add(args, ops, device, flush) -> tuple[float, str]:
+    """The norm that stands behind a branch: the branch's rows read, the fp32 stream read and written, its copy written."""
+    y = torch.randn(args.rows, args.width, device=device, dtype=torch.bfloat16)
+    stream = torch.randn(args.rows, args.width, device=device, dtype=torch.float32)
+    gain = torch.ones(args.width, device=device, dtype=torch.float32)
+
+    def run():
+        ops.scaled_norm_add(stream, y, gain, 1e-5, 0.5, torch.bfloat16)
+
+    us = _time(run, args.iters, args.warmup, flush)
+    nbytes = args.rows * args.width * (2 + 4 + 4 + 2)
+    return us, f"{nbytes / us / 1e6:.2f} TB/s"
+
+
+def mlstm_gates(args, ops, device, flush) -> tuple[float, str]:
+    """The gates' walk of a matrix memory over one portion of ``rows`` tokens: a chain of ``rows`` dependent steps per head."""
+    from types import SimpleNamespace
+
+    heads = args.heads
+    z = torch.randn(args.rows, 2 * heads, device=device, dtype=torch.float32)
+    bias = torch.zeros(heads, device=device, dtype=torch.float32)
+    state = torch.zeros(1, heads, device=device, dtype=torch.float32)
+    i32 = lambda v: torch.tensor(v, device=device, dtype=torch.int32)
+    ctx = SimpleNamespace(q_start=i32([0]), q_len=i32([args.rows]), state_slot=i32([0]), n_requests=1,
+                          decode_only=args.rows == 1, host_q_len=[args.rows])
+
+    def run():
+        ops.mlstm_gates(z, bias, bias, 15.0, heads, state, 0, ctx)
+
+    us = _time(run, args.iters, args.warmup, flush)
+    return us, f"{us * 1e3 / args.rows:.1f} ns per token of the chain"
+
+
 def silu_mul(args, ops, device, flush) -> tuple[float, str]:
     gu = torch.randn(args.rows, 2 * args.width, device=device, dtype=torch.bfloat16)
 
@@ -254,6 +289,8 @@ KERNELS = {
     "attention_prefill": attention_prefill,
     "gemm_tma": gemm_tma,
     "add_rmsnorm": add_rmsnorm,
+    "norm_add": norm_add,
+    "mlstm_gates": mlstm_gates,
     "silu_mul": silu_mul,
     "rope_write": rope_write,
     "sample": sample,
