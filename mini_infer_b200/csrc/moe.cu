@@ -42,7 +42,7 @@ __device__ __forceinline__ float mi_clamped_glu_value(float g, float u, float li
 // the logit, the weights the softmax over the chosen logits alone.  mode 1: scores are the softmax over all
 // experts (the logit orders alike); the chosen experts' scores are divided by their sum (+ 1e-20) and
 // multiplied by `scale`.  mode 2: scores are sigmoid(logit), the choice score adds `correction[e]` (may be
-// absent), the weights are the chosen experts' scores times `scale`, not renormalised.  With n_groups > 1
+// absent), the weights are the chosen experts' scores times `scale` (no division by their sum).  With n_groups > 1
 // the experts lie in n_groups equal groups of neighbours and only experts of the `keep` best groups (ties:
 // the lower index) can be chosen; a group counts as its best choice score (group_top2 = 0) or as the sum
 // of its two best (group_top2 = 1).

@@ -1594,7 +1594,7 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, all_scores: bo
     neighbours, a group counts as its best expert, and only the ``keep_groups`` best groups give experts.
     ``scores`` names the way outright: ``"chosen"``, ``"all"`` or ``"sigmoid"`` (scores are the logits'
     sigmoids; the choice adds ``correction`` (fp32 ``[experts]``) per expert; the weights are the chosen
-    scores times ``scale``, not renormalised).  ``group_top2``: a group counts as the sum of its two best
+    scores times ``scale``, with no division by their sum).  ``group_top2``: a group counts as the sum of its two best
     choice scores.  ``experts``: only the router's first ``experts`` rows are experts; the other rows ride
     along in the product and ``return_logits`` hands all logits back as a third result."""
     _cuda(x, router, correction)

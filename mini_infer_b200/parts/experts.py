@@ -17,7 +17,7 @@ class RoutedExperts(FeedForward):
     default), or their scores under the softmax over all experts, divided by the sum of these
     (+ 1e-20) and multiplied by ``route_scale`` (``scores`` ``"all"``), or (``scores`` ``"sigmoid"``) the
     scores are ``s = sigmoid(z)``, the choice goes by ``s + correction`` (``correction``: a tensor, one number
-    per expert) and the weights are the chosen ``s`` times ``route_scale``, not renormalised.  With
+    per expert) and the weights are the chosen ``s`` times ``route_scale`` (no division by their sum).  With
     ``groups`` > 1 the experts form that many equal groups of neighbours, a group counts as its best
     expert (``group_score`` ``"best"``, the default) or as the sum of its two best choice scores
     (``"top2"``), and only experts of the ``keep_groups`` best groups can be chosen.  The output is the

@@ -192,7 +192,7 @@ class ChunkAttention(ProjectedMixer):
     only gives its values away and has no ``vmix``.  With ``head_gate`` head
     ``h``'s output is multiplied by ``sigmoid(W_g x)_h``, one number per head.  With ``bias`` q, k and v
     have biases (added in fp32 before the norm).  With ``sink`` ``"learned"`` the softmax's denominator of head
-    ``h`` also holds ``exp(sink_h)``, a number that has no key and no value and is not scaled.  With
+    ``h`` also holds ``exp(sink_h)``: a logit of the head's own that enters the normaliser alone (no score scale).  With
     ``own_kv`` False the layer has no keys and values of its own (no ``k``, ``v``, ``k.norm``, no biases of
     theirs): it reads the cache layer that another layer with the same head counts wrote, with its own
     queries.  Scores, weights and sums are fp32 for either dtype.

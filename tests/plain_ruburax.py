@@ -119,7 +119,7 @@ def softmax_attention(h: torch.Tensor, W: dict, positions, m: dict, eps: float, 
     """Causal attention of ``heads`` query heads over ``kv_heads`` key/value heads (query head ``a`` reads
     key/value head ``a // (heads / kv_heads)``); queries and keys get an RMS norm over the head with a gain
     shared by the heads, then the rotation; the score is ``q . k * scale``.  With ``sink`` the softmax's
-    denominator also holds ``exp(sink_a)``, which has no key and no value.  ``keys_values``: another
+    denominator also holds ``exp(sink_a)``, a term with nothing behind it: it only takes weight away.  ``keys_values``: another
     layer's ``(k, v)`` in the place of this layer's own.  Returns ``(output, (k, v))``."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -202,7 +202,7 @@ def gated_unit(h: torch.Tensor, W: dict, prefix: str = "") -> torch.Tensor:
 def choose_experts(z: torch.Tensor, correction: torch.Tensor, router: dict):
     """One token: scores ``s = sigmoid(z)``, choice scores ``s + correction``.  With groups, a group's score
     is the sum of its two largest choice scores and only experts of the best ``keep`` groups stay in the
-    race.  Returns the ``top`` experts by choice score, their weights ``s * scale`` (not renormalised), and
+    race.  Returns the ``top`` experts by choice score, their weights ``s * scale`` (as they are, whatever they sum to), and
     how close the call was: the smallest gap between something taken and something left (groups, experts)."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(z)

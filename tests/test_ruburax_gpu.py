@@ -449,8 +449,8 @@ def test_matrix_memory_state_running_maximum_and_a_far_key(heads, dk, dv, cap, d
 def test_sigmoid_router_with_correction_groups_and_gated_shared_expert(E, top, ff, H, M, groups, scale, shared, dtype,
                                                                        bound):
     """The choice by sigmoid score plus correction within the groups whose two best choice scores sum highest
-    (corrections reach below zero, so an expert that is out must count as minus infinity, not as 0), the
-    weights without the correction and not renormalised, the weighted sum of the experts, and the shared
+    (corrections reach below zero: an excluded expert has to lose against every negative score, which a
+    placeholder of 0 would not), the weights free of the correction and of any division by their sum, the weighted sum of the experts, and the shared
     expert under its own sigmoid gate, against the plain token loop."""
     from mini_infer_b200.parts import PartSpec, build_part
 
